@@ -16,6 +16,6 @@ if [ "$1" = "ncu" ] || [ "$1" = "ncuonly" ]; then
   ncu --metrics gpu__time_duration.sum --clock-control none -s 1300 -c 700 --csv --log-file gpurun_out/launches.csv $CMD > gpurun_out/ncu.log 2>&1
   echo "ncu list rc=$?"
   $CMD > gpurun_out/plain2.log 2>&1 && \
-  ncu --set full --clock-control none --import-source on -k regex:gemm_kernel -s 460 -c 6 -o gpurun_out/prof_gemm $CMD > gpurun_out/ncu_full.log 2>&1
+  ncu --set full --clock-control none -k regex:gemm_kernel -s 460 -c 6 -o gpurun_out/prof_gemm $CMD > gpurun_out/ncu_full.log 2>&1
   echo "ncu full rc=$?"
 fi
