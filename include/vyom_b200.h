@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define VY_ABI_VERSION 7
+#define VY_ABI_VERSION 8
 
 #if defined(__GNUC__)
 #define VY_API __attribute__((visibility("default")))
@@ -609,6 +609,160 @@ typedef struct VyEmbed {
 
 VY_API int vy_embed_fwd(const VyEmbed* p);
 VY_API int vy_embed_bwd(const VyEmbed* p);
+
+/* ------------------------------------------------------------------------------------------
+ * Sequence-mixer family (vyomai_b200/csrc/seqmix.cu, linear_plain.cu): the kernels of the hybrid
+ * decoders served by vyomai_b200/models/gelutar.py — sliding-window attention with kept first
+ * tokens and a softmax sink over a paged cache, linear attention with a fixed decay, the gated
+ * delta rule, causal depthwise convolutions with carried taps, grouped / gated RMS norms, and a
+ * shape-agnostic fp32-accumulating linear layer. The reference has none of these.
+ *
+ * All of them work on a PACKED batch: the new tokens of the step's sequences are concatenated
+ * row-wise (no padding), described by
+ *   n_seqs                    sequences in the step
+ *   cu_tokens [n_seqs + 1]    device int32: rows [cu_tokens[s], cu_tokens[s+1]) belong to sequence s
+ *   pos0      [n_seqs]        device int32: position of the sequence's first new token (0 = start:
+ *                             recurrent state and convolution taps are taken as zero, not read)
+ *   slot      [n_seqs]        device int32: the sequence's row in the recurrent-state tensors
+ *   max_new                   longest run of new tokens in the step (sizes the grids)
+ * A step may mix sequences that start, continue with several tokens, or advance by one token.
+ * Statistics, scores, softmax, decays and recurrent state are fp32 whatever the I/O dtypes.
+ * ------------------------------------------------------------------------------------------ */
+enum { VY_UACT_NONE = 0, VY_UACT_RELU2 = 1, VY_UACT_SILU = 2, VY_UACT_SIGMOID = 3 };
+
+/* out = act(A W^T + bias) * scale + addend, any M, N, K, any alignment; fp32 FMA accumulation (true fp32: no tf32). A and
+ * W may have different dtypes (fp32 activations against bf16 weights). addend may alias out. scale 0 = 1. */
+typedef struct VyLinear {
+  int32_t M, N, K;
+  const void* A; int64_t lda; int32_t a_dtype;
+  const void* W; int64_t ldw; int32_t w_dtype;
+  const void* bias; int32_t bias_dtype;
+  const void* addend; int64_t ld_addend; int32_t addend_dtype;
+  int32_t act;
+  float scale;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyLinear;
+VY_API int vy_linear_plain(const VyLinear* p);
+
+/* Grouped RMS norm with optional weight, gate, row gather and accumulation. Row r = (token r / groups, group r % groups),
+ * source token st = row_index ? row_index[token] : token:
+ *   xn[c]  = x[st * ldx + group * width + c] / sqrt(mean_c(x^2) + eps)
+ *   y[c]   = coef * xn[c] * (w_mode == 0 ? 1 : w_mode == 1 ? weight[c] : 1 + weight[c])
+ *                 * (gate ? (gate_act == VY_UACT_SIGMOID ? sigmoid(gate[st * ld_gate + group * width + c]) : gate[..]) : 1)
+ *   out[token * ld_out + group * width + c] = (accumulate ? out[..] : 0) + y[c]
+ * weight is [width], shared by the groups. coef 0 = 1. */
+typedef struct VyRmsNorm {
+  int64_t tokens;
+  int32_t groups, width;
+  const int32_t* row_index;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  const void* weight; int32_t w_dtype; int32_t w_mode;
+  const void* gate; int64_t ld_gate; int32_t gate_dtype; int32_t gate_act;
+  float eps, coef;
+  int32_t accumulate;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyRmsNorm;
+VY_API int vy_rms_norm(const VyRmsNorm* p);
+
+/* out[r, c] = act(x[r, c]) with a dtype change (the activation between two tensor-core GEMMs, computed in fp32). */
+VY_API int vy_unary(int64_t rows, int32_t cols, const void* x, int64_t ldx, int32_t x_dtype, int32_t act, void* out, int64_t ld_out,
+                    int32_t out_dtype, void* stream);
+
+/* out[r, :] = scale * table[ids[r], :] (ids int32; an id outside [0, vocab) gives a zero row). */
+VY_API int vy_embed_rows(int32_t rows, int32_t width, int32_t vocab, const int32_t* ids, const void* table, int64_t ld_table,
+                         int32_t table_dtype, float scale, void* out, int64_t ld_out, int32_t out_dtype, void* stream);
+
+/* Writes the step's keys and values into paged pools [num_blocks, block_size, kv_heads, dim | vdim]: the row of
+ * position p of sequence s is block_table[s * table_width + p / block_size] * block_size + p % block_size. */
+typedef struct VyKvWrite {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const int32_t* block_table; int32_t table_width, block_size;
+  const void* k; int64_t ldk; const void* v; int64_t ldv; int32_t in_dtype;
+  int32_t k_width, v_width; /* kv_heads * dim, kv_heads * vdim */
+  void* k_pool; void* v_pool; int32_t pool_dtype;
+  void* stream;
+} VyKvWrite;
+VY_API int vy_kv_page_write(const VyKvWrite* p);
+
+/* Windowed attention over the paged pools. The query at position i of sequence s sees key j iff
+ * j <= i and (i - j < window or j < keep_first); window <= 0 = no window (plain causal). Kept keys enter with their own
+ * rows of the cache; positions do not enter the score otherwise. score = (q . k) * scale. With `sink` (one number per
+ * query head) the softmax denominator also holds exp(sink[h]): it has no key and no value. With `gate` the head's
+ * output is multiplied by sigmoid(gate[token, h]). Query head h reads kv head h / (heads / kv_heads). The step's own
+ * keys must already be in the pools (vy_kv_page_write). One warp per query when a sequence brings several tokens; the
+ * four warps of a CTA split the keys of a single-token query (decode). */
+typedef struct VyWinAttn {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const int32_t* block_table; int32_t table_width, block_size;
+  const void* q; int64_t ldq; int32_t q_dtype;
+  const void* k_pool; const void* v_pool; int32_t pool_dtype;
+  int32_t heads, kv_heads, dim, vdim;
+  float scale;
+  int32_t window, keep_first;
+  const void* sink; int32_t sink_dtype;
+  const void* gate; int64_t ld_gate; int32_t gate_dtype;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyWinAttn;
+VY_API int vy_window_attn(const VyWinAttn* p);
+
+/* Depthwise causal convolution over time with carried taps, then an activation:
+ *   y[t, c] = act(sum_d w[c, taps - 1 - d] * x[t - d, c]),  d = 0 .. taps - 1
+ * x[t - d] before the step's first row comes from state[slot, c, :] (the sequence's last taps - 1 inputs, oldest first;
+ * zeros when pos0 == 0). After the outputs are written the state is advanced to the last taps - 1 inputs of the sequence.
+ * out must not alias x. taps <= 16. */
+typedef struct VyCausalConv {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0; const int32_t* slot;
+  int32_t channels, taps;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  const void* w; int32_t w_dtype; /* [channels, taps] */
+  float* state;                    /* [slots, channels, taps - 1] */
+  int32_t act;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyCausalConv;
+VY_API int vy_causal_conv(const VyCausalConv* p);
+
+/* Linear attention with one fixed decay per head, state carried per sequence:
+ *   S_t = decay[h] * S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t      (S is dim x vdim, fp32)
+ * q, k, v pass `in_act` (VY_UACT_*) when they are read. state is [slots, heads, dim, vdim]. dim <= 256. */
+typedef struct VyLinAttn {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0; const int32_t* slot;
+  const void* q; int64_t ldq; const void* k; int64_t ldk; const void* v; int64_t ldv; int32_t in_dtype; int32_t in_act;
+  int32_t heads, dim, vdim;
+  const float* decay; /* [heads], device */
+  float* state;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyLinAttn;
+VY_API int vy_linear_attn(const VyLinAttn* p);
+
+/* Gated delta rule, state carried per sequence. Per head h (q / k head h / (heads / kv_heads)) and token:
+ *   qh = q / sqrt(sum q^2 + unit_eps) * dim^-1/2,  kh = k / sqrt(sum k^2 + unit_eps)
+ *   g[i] = exp(-exp(a_log[h]) * softplus(a[t, h * dim + i])),  beta = sigmoid(b[t, h])
+ *   S <- diag(g) S;  u = beta * (v - S^T kh);  S <- S + kh u^T;  o = S^T qh
+ * q, k, v are the (already convolved and activated) projections; state is [slots, heads, dim, vdim] fp32. dim <= 256. */
+typedef struct VyDeltaRule {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0; const int32_t* slot;
+  const void* q; int64_t ldq; const void* k; int64_t ldk; const void* v; int64_t ldv; int32_t in_dtype;
+  const void* a; int64_t ld_a; int32_t a_dtype;
+  const void* b; int64_t ld_b; int32_t b_dtype;
+  const void* a_log; int32_t a_log_dtype;
+  int32_t heads, kv_heads, dim, vdim;
+  float unit_eps;
+  float* state;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyDeltaRule;
+VY_API int vy_delta_rule(const VyDeltaRule* p);
+
 
 /* vy_patchify — NCHW pixels -> [B * (H/ph) * (W/pw), C*ph*pw] patch rows, (c, i, j) order with j
  * fastest: the im2col of the stride==kernel nn.Conv2d at VyomAI/models/vision_encoder.py:83-88,114

@@ -15,3 +15,6 @@ from .models.custom_transformer import ModelForCausalLM  # noqa: F401  (inferenc
 from .layers.adapters import DoraLinear, LoraLinear  # noqa: F401
 from .generation_utils import generate, generate_multimodel, generate_seq2seq  # noqa: F401
 from .paged import ContinuousBatchEngine, PagedKVManager, SequenceState  # noqa: F401  (Examples/simple_vllm.ipynb)
+from .paged import HybridBatchEngine, HybridCacheManager, HybridSequence  # noqa: F401  (packed steps over pages + state slots)
+from .models.gelutar import GelutarConfig, GelutarForCausalLM  # noqa: F401
+from .registry import load_model, register_model  # noqa: F401

@@ -198,6 +198,13 @@ int vy_abi_sizeof(const char* name) {
   VY_SZ(VyDpGroup);
   VY_SZ(VyDpReduce);
   VY_SZ(VyDpAdamW);
+  VY_SZ(VyLinear);
+  VY_SZ(VyRmsNorm);
+  VY_SZ(VyKvWrite);
+  VY_SZ(VyWinAttn);
+  VY_SZ(VyCausalConv);
+  VY_SZ(VyLinAttn);
+  VY_SZ(VyDeltaRule);
 #undef VY_SZ
   return -1;
 }

@@ -857,3 +857,182 @@ def adamw(param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_dec
               lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps), weight_decay=float(weight_decay),
               step=int(step), step_ptr=_ptr(step_ptr), grad_sqnorm=_ptr(grad_sqnorm), max_grad_norm=float(max_grad_norm), grad_div=float(grad_div),
               stream=_stream())
+
+
+# ---- sequence-mixer family (csrc/seqmix.cu, csrc/linear_plain.cu): packed batches, fp32 statistics and state ----
+UACT = {None: C["VY_UACT_NONE"], "none": C["VY_UACT_NONE"], "relu2": C["VY_UACT_RELU2"], "silu": C["VY_UACT_SILU"],
+        "sigmoid": C["VY_UACT_SIGMOID"]}
+W_MODE = {None: 0, "plain": 1, "one_plus": 2}
+
+
+class PackedBatch:
+    """Device-side description of one step's packed rows: `cu_tokens` [n + 1], `pos0` [n], `slot` [n] (int32) and, for models
+    with attention layers, `block_table` [n, table_width] (int32) over pages of `block_size` positions."""
+
+    def __init__(self, cu_tokens: torch.Tensor, pos0: torch.Tensor, slot: torch.Tensor, max_new: int,
+                 block_table: Optional[torch.Tensor] = None, block_size: int = 0):
+        self.cu_tokens, self.pos0, self.slot, self.max_new = cu_tokens, pos0, slot, int(max_new)
+        self.block_table, self.block_size = block_table, int(block_size)
+        self.n_seqs = pos0.numel()
+
+    def _kw(self, pages: bool = False, slots: bool = True) -> dict:
+        kw = dict(n_seqs=self.n_seqs, max_new=self.max_new, cu_tokens=self.cu_tokens.data_ptr(), pos0=self.pos0.data_ptr())
+        if slots:
+            kw["slot"] = self.slot.data_ptr()
+        if pages:
+            if self.block_table is None:
+                raise _lib.VyomError("this step carries no block table")
+            kw.update(block_table=self.block_table.data_ptr(), table_width=self.block_table.shape[1], block_size=self.block_size)
+        return kw
+
+
+def _rows2d(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise _lib.VyomError(f"{what}: expected a 2-d tensor with unit column stride, got shape {tuple(t.shape)} strides {t.stride()}")
+
+
+def linear_plain(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: Optional[str] = None, scale: float = 1.0,
+                 addend: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out = act(x @ w.T + bias) * scale + addend with fp32 FMA accumulation (any shape; x and w may differ in dtype)."""
+    _need_cuda(x, w, bias, addend, out)
+    _rows2d(x, "linear_plain x")
+    _rows2d(w, "linear_plain w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise _lib.VyomError(f"linear_plain: inner dimensions differ ({K} vs {w.shape[1]})")
+    if out is None:
+        out = torch.empty((M, N), device=x.device, dtype=out_dtype or x.dtype)
+    _rows2d(out, "linear_plain out")
+    _lib.call("vy_linear_plain", "VyLinear", M=M, N=N, K=K, A=x.data_ptr(), lda=x.stride(0), a_dtype=_dt(x), W=w.data_ptr(),
+              ldw=w.stride(0), w_dtype=_dt(w), bias=_ptr(bias), bias_dtype=_dt(bias) if bias is not None else 0, addend=_ptr(addend),
+              ld_addend=addend.stride(0) if addend is not None else 0, addend_dtype=_dt(addend) if addend is not None else 0,
+              act=UACT[act], scale=float(scale), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_mode: Optional[str] = "plain", groups: int = 1,
+             gate: Optional[torch.Tensor] = None, gate_act: Optional[str] = "sigmoid", coef: float = 1.0, accumulate: bool = False,
+             row_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Grouped RMS norm (fp32 statistics): each row of x is `groups` runs of width x.shape[1] / groups, every run normalised on
+    its own, times the weight (plain or 1 + w, shared by the runs), times an optional (sigmoid) gate, times coef; optionally
+    added into `out`, optionally reading rows x[row_index]."""
+    _need_cuda(x, weight, gate, out, row_index)
+    _rows2d(x, "rms_norm x")
+    tokens = x.shape[0] if row_index is None else row_index.numel()
+    if x.shape[1] % groups:
+        raise _lib.VyomError("rms_norm: row width is not a multiple of groups")
+    width = x.shape[1] // groups
+    if weight is None:
+        w_mode = None
+    elif weight.numel() != width or not weight.is_contiguous():
+        raise _lib.VyomError(f"rms_norm: weight has {weight.numel()} elements, expected {width}")
+    if out is None:
+        if accumulate:
+            raise _lib.VyomError("rms_norm: accumulate needs `out`")
+        out = torch.empty((tokens, x.shape[1]), device=x.device, dtype=out_dtype or x.dtype)
+    _rows2d(out, "rms_norm out")
+    if gate is not None:
+        _rows2d(gate, "rms_norm gate")
+    _lib.call("vy_rms_norm", "VyRmsNorm", tokens=tokens, groups=groups, width=width, row_index=_ptr(row_index), x=x.data_ptr(),
+              ldx=x.stride(0), x_dtype=_dt(x), weight=_ptr(weight), w_dtype=_dt(weight) if weight is not None else 0,
+              w_mode=W_MODE[w_mode], gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0,
+              gate_dtype=_dt(gate) if gate is not None else 0, gate_act=UACT[gate_act], eps=float(eps), coef=float(coef),
+              accumulate=1 if accumulate else 0, out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def unary(x: torch.Tensor, act: Optional[str], out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(x, out)
+    _rows2d(x, "unary x")
+    if out is None:
+        out = torch.empty(x.shape, device=x.device, dtype=out_dtype)
+    _lib.call_raw("vy_unary", x.shape[0], x.shape[1], x.data_ptr(), x.stride(0), _dt(x), UACT[act], out.data_ptr(), out.stride(0), _dt(out),
+                  _stream())
+    return out
+
+
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    _need_cuda(ids, table)
+    if ids.dtype != torch.int32:
+        raise _lib.VyomError("embed_rows: ids must be int32")
+    out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=out_dtype)
+    _lib.call_raw("vy_embed_rows", ids.numel(), table.shape[1], table.shape[0], ids.data_ptr(), table.data_ptr(), table.stride(0), _dt(table),
+                  float(scale), out.data_ptr(), out.stride(0), _dt(out), _stream())
+    return out
+
+
+def kv_page_write(batch: PackedBatch, k: torch.Tensor, v: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor) -> None:
+    _need_cuda(k, v, k_pool, v_pool)
+    _rows2d(k, "kv_page_write k")
+    _rows2d(v, "kv_page_write v")
+    if k.dtype != v.dtype or k_pool.dtype != v_pool.dtype or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise _lib.VyomError("kv_page_write: k / v and the two pools must share a dtype each; pools contiguous")
+    _lib.call("vy_kv_page_write", "VyKvWrite", k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0), in_dtype=_dt(k),
+              k_width=k.shape[1], v_width=v.shape[1], k_pool=k_pool.data_ptr(), v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool),
+              stream=_stream(), **batch._kw(pages=True, slots=False))
+
+
+def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
+                vdim: int, scale: float, window: int, keep_first: int, sink: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Attention of the step's queries over the paged pools (which already hold the step's keys): causal, restricted to the last
+    `window` positions plus the first `keep_first` ones, optional per-head sink in the softmax denominator, optional per-head
+    sigmoid output gate."""
+    _need_cuda(q, k_pool, v_pool, sink, gate)
+    _rows2d(q, "window_attn q")
+    out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or q.dtype)
+    _lib.call("vy_window_attn", "VyWinAttn", q=q.data_ptr(), ldq=q.stride(0), q_dtype=_dt(q), k_pool=k_pool.data_ptr(),
+              v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale),
+              window=int(window), keep_first=int(keep_first), sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
+              gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0, gate_dtype=_dt(gate) if gate is not None else 0,
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw(pages=True, slots=False))
+    return out
+
+
+def causal_conv(batch: PackedBatch, x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, act: Optional[str] = "silu",
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Depthwise causal convolution over time (w [channels, taps], last column = current token) + activation; `state`
+    [slots, channels, taps - 1] fp32 carries each sequence's last inputs and is advanced."""
+    _need_cuda(x, w, state)
+    _rows2d(x, "causal_conv x")
+    ch, taps = w.shape
+    if x.shape[1] != ch or not w.is_contiguous() or state.dtype != torch.float32 or not state.is_contiguous():
+        raise _lib.VyomError("causal_conv: shapes / layout")
+    out = torch.empty((x.shape[0], ch), device=x.device, dtype=out_dtype or x.dtype)
+    _lib.call("vy_causal_conv", "VyCausalConv", channels=ch, taps=taps, x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), w=w.data_ptr(),
+              w_dtype=_dt(w), state=state.data_ptr(), act=UACT[act], out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out),
+              stream=_stream(), **batch._kw())
+    return out
+
+
+def linear_attn(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, *,
+                heads: int, dim: int, vdim: int, in_act: Optional[str] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """S = decay_h S + k v^T, o = S^T q per head, state [slots, heads, dim, vdim] fp32 carried per sequence."""
+    _need_cuda(q, k, v, decay, state)
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _rows2d(t, f"linear_attn {n}")
+    if decay.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous():
+        raise _lib.VyomError("linear_attn: decay and state are fp32")
+    out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or torch.float32)
+    _lib.call("vy_linear_attn", "VyLinAttn", q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
+              in_dtype=_dt(q), in_act=UACT[in_act], heads=heads, dim=dim, vdim=vdim, decay=decay.data_ptr(), state=state.data_ptr(),
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw())
+    return out
+
+
+def delta_rule(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor, a_log: torch.Tensor,
+               state: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Gated delta rule over unit-norm q / k with per-channel decay exp(-exp(a_log) softplus(a)) and write strength sigmoid(b)."""
+    _need_cuda(q, k, v, a, b, a_log, state)
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (a, "a"), (b, "b")):
+        _rows2d(t, f"delta_rule {n}")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise _lib.VyomError("delta_rule: state is fp32")
+    out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or torch.float32)
+    _lib.call("vy_delta_rule", "VyDeltaRule", q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
+              in_dtype=_dt(q), a=a.data_ptr(), ld_a=a.stride(0), a_dtype=_dt(a), b=b.data_ptr(), ld_b=b.stride(0), b_dtype=_dt(b),
+              a_log=a_log.data_ptr(), a_log_dtype=_dt(a_log), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, unit_eps=float(unit_eps),
+              state=state.data_ptr(), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw())
+    return out

@@ -188,3 +188,224 @@ class ContinuousBatchEngine:
                 self.kv_mgr.free(s)
                 del self.active[s.id]
         return finished
+
+
+# ==== hybrid models: pages for attention layers, state slots for recurrent layers, packed steps ====
+class LayerCacheView:
+    """What one mixer sees of the manager: its page pools (attention) and / or its per-slot state tensors (recurrences)."""
+
+    def __init__(self):
+        self.k_pool: torch.Tensor = None
+        self.v_pool: torch.Tensor = None
+        self.states: Dict[str, torch.Tensor] = {}
+
+
+class HybridSequence:
+    """One request of a hybrid model: its tokens (host side), how many of them the cache already holds, the pages that hold its
+    keys / values and the slot that holds its recurrent state."""
+
+    def __init__(self, sid, tokens: List[int], max_total_len: int = 0):
+        self.id, self.tokens, self.max_total_len = sid, list(tokens), max_total_len
+        self.num_cached = 0
+        self.blocks: List[int] = []
+        self.slot = -1
+
+
+class HybridCacheManager:
+    """Pages and state slots for a model whose layers declare `cache_specs()` (per layer, per mixer:
+    {"pages": (kv_heads, dim, vdim) | None, "states": {name: per-slot shape}}). Attention mixers get pools
+    [num_blocks, block_size, kv_heads, dim | vdim] addressed through each sequence's block list — the same page scheme as
+    PagedKVManager above; recurrent mixers get fp32 tensors [num_slots, *shape] addressed by the sequence's slot. Both
+    grow on demand, so `max_tokens` / `max_seqs` are sizing hints, not limits. A slot or page handed out again is not
+    cleared: a sequence whose first position is 0 never reads what its slot held, and pages are written before they are
+    read."""
+
+    def __init__(self, model, max_tokens: int = 4096, block_size: int = 16, max_seqs: int = 8, device=None):
+        self.block_size = int(block_size)
+        self.device = torch.device(device or model.device)
+        self._specs = model.cache_specs()
+        self.has_pages = any(s["pages"] for layer in self._specs for s in layer)
+        self.views: List[List[LayerCacheView]] = [[LayerCacheView() for _ in layer] for layer in self._specs]
+        self.num_blocks = 0
+        self.num_slots = 0
+        self.free_blocks: deque = deque()
+        self.free_slots: deque = deque()
+        self._grow_slots(max(1, int(max_seqs)))
+        if self.has_pages:
+            self._grow_blocks((max(1, int(max_tokens)) + self.block_size - 1) // self.block_size + max(1, int(max_seqs)))
+
+    def _grow_blocks(self, n_more: int) -> None:
+        new_total = self.num_blocks + n_more
+        for layer, views in zip(self._specs, self.views):
+            for spec, view in zip(layer, views):
+                if not spec["pages"]:
+                    continue
+                g, dk, dv = spec["pages"]
+                dt = spec.get("kv_dtype", torch.float32)
+                for name, d in (("k_pool", dk), ("v_pool", dv)):
+                    new = torch.zeros((new_total, self.block_size, g, d), device=self.device, dtype=dt)
+                    old = getattr(view, name)
+                    if old is not None:
+                        new[: self.num_blocks] = old
+                    setattr(view, name, new)
+        self.free_blocks.extend(range(self.num_blocks, new_total))
+        self.num_blocks = new_total
+
+    def _grow_slots(self, n_more: int) -> None:
+        new_total = self.num_slots + n_more
+        for layer, views in zip(self._specs, self.views):
+            for spec, view in zip(layer, views):
+                for name, shape in spec["states"].items():
+                    new = torch.zeros((new_total,) + tuple(shape), device=self.device, dtype=torch.float32)
+                    if name in view.states:
+                        new[: self.num_slots] = view.states[name]
+                    view.states[name] = new
+        self.free_slots.extend(range(self.num_slots, new_total))
+        self.num_slots = new_total
+
+    def blocks_for(self, n_tokens: int) -> int:
+        return (n_tokens + self.block_size - 1) // self.block_size if self.has_pages else 0
+
+    def can_allocate(self, n_tokens: int) -> bool:
+        """Room for a NEW sequence of n_tokens without growing?"""
+        return len(self.free_blocks) >= self.blocks_for(n_tokens) and len(self.free_slots) >= 1
+
+    def allocate(self, seq: HybridSequence, n_tokens: int) -> None:
+        """Makes `seq` own a slot and enough pages for its first n_tokens positions (growing the pools if they ran out)."""
+        if seq.slot < 0:
+            if not self.free_slots:
+                self._grow_slots(self.num_slots)
+            seq.slot = self.free_slots.popleft()
+        need = self.blocks_for(n_tokens) - len(seq.blocks)
+        if need > len(self.free_blocks):
+            self._grow_blocks(max(need - len(self.free_blocks), self.num_blocks // 2, 1))
+        for _ in range(max(need, 0)):
+            seq.blocks.append(self.free_blocks.popleft())
+
+    def free(self, seq: HybridSequence) -> None:
+        self.free_blocks.extend(seq.blocks)
+        seq.blocks = []
+        if seq.slot >= 0:
+            self.free_slots.append(seq.slot)
+            seq.slot = -1
+        seq.num_cached = 0
+
+
+class HybridBatchEngine:
+    """Continuous batching for hybrid models, the counterpart of ContinuousBatchEngine for models with a packed `step`
+    (models/gelutar.py): every engine iteration is ONE model step over the concatenated new tokens of all live
+    sequences — whole prompts of the sequences that start, one token of those that decode — so nothing is padded and
+    a sequence's logits do not depend on its neighbours. `step()` is the greedy generation loop (waiting room, eos /
+    length retirement as above); `feed()` / `release()` advance named sequences by GIVEN tokens and return the logits of
+    chosen rows (replaying a recorded trace, scoring, teacher forcing) through the same step and manager."""
+
+    def __init__(self, model, cache_mgr: HybridCacheManager, max_batch_size: int = 16, eos_token_ids: Iterable[int] = ()):
+        self.model, self.cache = model, cache_mgr
+        self.device = cache_mgr.device
+        self.max_batch = max_batch_size
+        self.eos = set(int(t) for t in eos_token_ids)
+        self.active: Dict[object, HybridSequence] = {}
+        self.waiting_room: deque = deque()
+        self.id_gen = itertools.count()
+
+    # ---- the shared step ----
+    @torch.no_grad()
+    def _run(self, work: List, want: List[List[int]]) -> torch.Tensor:
+        """work: [(sequence, new tokens)]; want[i]: offsets among sequence i's new tokens whose logits are returned
+        (in order). Extends the sequences' pages, runs the model step, advances `num_cached`."""
+        mgr = self.cache
+        n = len(work)
+        cu, pos0, slot, ids, rows = [0], [], [], [], []
+        for (seq, toks), w in zip(work, want):
+            if not toks:
+                raise ValueError("a sequence in a step needs at least one new token")
+            mgr.allocate(seq, seq.num_cached + len(toks))
+            for o in w:
+                if not 0 <= o < len(toks):
+                    raise ValueError(f"wanted offset {o} outside the {len(toks)} new tokens")
+                rows.append(cu[-1] + o)
+            pos0.append(seq.num_cached)
+            slot.append(seq.slot)
+            ids += [int(t) for t in toks]
+            cu.append(cu[-1] + len(toks))
+        width = max(1, max(len(seq.blocks) for seq, _ in work))
+        table = []
+        for seq, _ in work:
+            table += seq.blocks + [0] * (width - len(seq.blocks))
+        flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        o = 0
+
+        def take(k):
+            nonlocal o
+            t = flat[o:o + k]
+            o += k
+            return t
+        cu_t, pos_t, slot_t = take(n + 1), take(n), take(n)
+        table_t = take(n * width).view(n, width)
+        ids_t, rows_t = take(len(ids)), take(len(rows))
+        batch = ops.PackedBatch(cu_t, pos_t, slot_t, max(len(t) for _, t in work), table_t if mgr.has_pages else None, mgr.block_size)
+        logits = self.model.step(ids_t, batch, mgr.views, rows_t if rows else None)
+        for seq, toks in work:
+            seq.num_cached += len(toks)
+        return logits
+
+    # ---- given tokens ----
+    def feed(self, entries: List) -> torch.Tensor:
+        """entries: [(key, tokens, want offsets)]; unknown keys start new sequences. Returns fp32 logits [sum(len(want)), vocab]
+        (None when nothing is wanted)."""
+        work, want = [], []
+        for key, toks, w in entries:
+            seq = self.active.get(key)
+            if seq is None:
+                seq = self.active[key] = HybridSequence(key, [])
+            seq.tokens += list(toks)
+            work.append((seq, list(toks)))
+            want.append(list(w))
+        return self._run(work, want)
+
+    def release(self, keys: Iterable) -> None:
+        for key in keys:
+            seq = self.active.pop(key, None)
+            if seq is not None:
+                self.cache.free(seq)
+
+    # ---- greedy generation ----
+    def add_sequence(self, prompt_ids: List[int], max_gen_len: int = 128) -> int:
+        sid = next(self.id_gen)
+        self.waiting_room.append(HybridSequence(sid, prompt_ids, len(prompt_ids) + max_gen_len))
+        return sid
+
+    def _try_schedule_waiting(self) -> None:
+        while self.waiting_room and len(self.active) < self.max_batch:
+            seq = self.waiting_room[0]
+            if self.active and not self.cache.can_allocate(len(seq.tokens)):
+                break  # pools full: retry after some sequence retires (an empty engine grows the pools instead)
+            self.waiting_room.popleft()
+            self.active[seq.id] = seq
+
+    def step(self) -> Dict[int, List[int]]:
+        """One iteration: admit waiting sequences, run prompts and single tokens as one packed step, pick each sequence's next
+        token greedily, retire finished sequences. Returns {sequence id: all its tokens} for those that finished."""
+        self._try_schedule_waiting()
+        if not self.active:
+            return {}
+        seqs = list(self.active.values())
+        work = [(s, s.tokens[s.num_cached:]) for s in seqs]
+        logits = self._run(work, [[len(t) - 1] for _, t in work])
+        nxt = ops.argmax_rows(logits).tolist()
+        finished: Dict[int, List[int]] = {}
+        for s, t in zip(seqs, nxt):
+            s.tokens.append(int(t))
+            if int(t) in self.eos or len(s.tokens) >= s.max_total_len:
+                finished[s.id] = list(s.tokens)
+                self.cache.free(s)
+                del self.active[s.id]
+        return finished
+
+    def generate(self, prompts: List[List[int]], max_new_tokens: int = 16) -> List[List[int]]:
+        """Greedy continuations of `prompts` (all queued at once; the waiting room and the batch limit decide the schedule)."""
+        sids = [self.add_sequence(p, max_new_tokens) for p in prompts]
+        done: Dict[int, List[int]] = {}
+        while self.active or self.waiting_room:
+            done.update(self.step())
+        return [done[s] for s in sids]
