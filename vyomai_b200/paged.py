@@ -332,7 +332,9 @@ class HybridBatchEngine:
         table = []
         for seq, _ in work:
             table += seq.blocks + [0] * (width - len(seq.blocks))
-        flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32)
+        if self.device.type == "cuda":   # one pinned staging buffer, one host-to-device copy per step
+            flat = flat.pin_memory().to(self.device, non_blocking=True)
         o = 0
 
         def take(k):
