@@ -357,7 +357,7 @@ class DecodeCfg:  # BASELINE config 3: GPT-style CLM, kv-cache, prefill 512 + gr
     eos_token_id = 2
 
 
-def decode_config3(dev, attn, batch=32, prefill=512, new_tokens=256):
+def decode_config3(dev, attn, batch=32, prefill=512, new_tokens=256, base=None, kv_heads=4, tag="decoder_clm_L4"):
     """Prefill + greedy decode of BASELINE config 3 through DecoderModel.generate (static cache, one CUDA-graph replay per
     token). Returns prefill tok/s, decode tok/s (device time of the replayed steps), the HBM roofline fraction of a decode
     step (algorithmic bytes = every weight but the embedding table + the kv-cache rows read, at the mean context) and
@@ -365,7 +365,8 @@ def decode_config3(dev, attn, batch=32, prefill=512, new_tokens=256):
     import io
     from contextlib import redirect_stdout
     from vyomai_b200 import DecoderModel
-    cfg = type("Cfg3", (DecodeCfg,), {"num_key_value_heads": 4})() if attn == "gqa" else DecodeCfg()
+    base = base or DecodeCfg
+    cfg = type("Cfg3", (base,), {"num_key_value_heads": kv_heads})() if attn == "gqa" else base()
     torch.manual_seed(0)
     with redirect_stdout(io.StringIO()):
         model = DecoderModel(cfg, "rope", "gqa" if attn == "gqa" else None)
@@ -373,7 +374,7 @@ def decode_config3(dev, attn, batch=32, prefill=512, new_tokens=256):
     B, P, N = batch, prefill, new_tokens
     ids = torch.randint(3, cfg.vocab_size, (B, P), device=dev)
     mask = torch.ones((B, P), device=dev, dtype=torch.long)
-    hkv = 4 if attn == "gqa" else 12
+    hkv = kv_heads if attn == "gqa" else cfg.num_attention_heads
     model.generate(ids, mask, max_len=N, use_cache=True, use_static_cache=True)  # warm-up: tunes the GEMMs, captures the graph
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -397,7 +398,7 @@ def decode_config3(dev, attn, batch=32, prefill=512, new_tokens=256):
     n_params = sum(p.numel() for n, p in model.named_parameters() if "word_embeddings" not in n)
     step_bytes = 2.0 * n_params + 2.0 * B * cfg.num_hidden_layers * 2 * hkv * (P + N / 2) * 64
     hbm = peaks()[0]
-    return {"workload": f"decoder_clm_L4_{attn}_B{B}_prefill{P}_decode{N}_bf16_staticcache",
+    return {"workload": f"{tag}_{attn}_B{B}_prefill{P}_decode{N}_bf16_staticcache",
             "prefill_tok_per_s": B * P / (pre_ms / 1e3), "decode_tok_per_s": B / (step_us * 1e-6), "decode_us_per_step": step_us,
             "decode_step_algorithmic_MB": step_bytes / 1e6, "decode_hbm_frac": step_bytes / (step_us * 1e-6) / 1e9 / hbm,
             "generate_tok_per_s_wall": B * N / wall, "tokens_checked": int(out.shape[1]),
@@ -902,6 +903,167 @@ def run_ours(args):
         os._exit(0)
 
 
+
+# ------------------------------------------------------------------------------------------------
+# --workload hybrid: the Gelutar hybrid decoder beside DecoderModel at equal width / depth / vocabulary
+# ------------------------------------------------------------------------------------------------
+HYBRID_KERNELS = ("linear_attn_chunk", "linear_attn", "delta_rule", "window_attn", "causal_conv", "rms_norm", "kv_page_write", "qk_norm_write",
+                  "linear_plain", "unary", "embed_rows", "gemm_skinny", "gemm_kernel", "attn_fwd", "attn_decode", "add_layernorm", "argmax")
+
+
+def hybrid_config(width, layers=8, vocab=32768, window=512):
+    """A realistic layer stack: three fixed-decay linear-attention layers, then one parallel (windowed softmax + gated delta) layer,
+    repeated; 128-wide heads, feed-forward 4 x width."""
+    H = width // 128
+    lin = {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(H - 1, 1)) for i in range(H)]},
+           "mlp": {"kind": "dense", "ff": 4 * width}}
+    par = {"type": "parallel", "mixer": {"left": {"heads": H, "kv_heads": max(H // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                  "mask": {"size": window, "keep_first": 4}},
+                                         "right": {"heads": H, "kv_heads": max(H // 2, 1), "dim": 128, "vdim": 128, "conv": 4}},
+           "mlp": {"kind": "dense", "ff": 4 * width}}
+    return {"architecture": "Gelutar", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [par if i % 4 == 3 else lin for i in range(layers)]}
+
+
+def _kernel_table(fn, names=HYBRID_KERNELS):
+    """Device time per kernel family of one call of fn (CUPTI through torch.profiler): {fragment: {"calls", "ms"}}."""
+    from collections import defaultdict
+    torch.cuda.synchronize()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        fn()
+        torch.cuda.synchronize()
+    agg = defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if ev.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        fam = next((n for n in names if n in ev.name), "other")
+        agg[fam][0] += 1
+        agg[fam][1] += ev.device_time_total
+    return {k: {"calls": n, "ms": round(t / 1e3, 4)} for k, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+
+
+def measure_hybrid(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, decode_steps=64, steps=5, warmup=3):
+    from vyomai_b200 import GelutarConfig, GelutarForCausalLM, HybridBatchEngine, HybridCacheManager
+    cfgd = hybrid_config(width)
+    cfg = GelutarConfig(cfgd)
+    model = GelutarForCausalLM(cfg, GelutarForCausalLM.random_weights(cfg, seed=0, low_rank=64), dtype=torch.bfloat16, device=dev,
+                               kv_dtype=torch.float32)
+    hbm, tf_burst, _, src = peaks()
+    g = torch.Generator().manual_seed(1)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2, rewritten between timed iterations
+    out = {"width": width, "layers": [L["type"] for L in cfgd["layers"]], "vocab": cfg.vocab, "peaks": src}
+
+    # prefill: batch_prefill prompts of `prompt` tokens as one packed step, pinned host ids -> device inside the timed region
+    mgr = HybridCacheManager(model, max_tokens=batch_decode * (prompt + decode_steps + 16), block_size=16, max_seqs=batch_decode)
+    eng = HybridBatchEngine(model, mgr)
+    prompts = [torch.randint(0, cfg.vocab, (prompt,), generator=g).tolist() for _ in range(batch_decode)]
+
+    def prefill(n):
+        lg = eng.feed([(i, prompts[i], [prompt - 1]) for i in range(n)])
+        return lg
+
+    times = []
+    for it in range(warmup + steps):
+        flush.fill_(it)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        prefill(batch_prefill)
+        e1.record()
+        torch.cuda.synchronize()
+        eng.release(range(batch_prefill))
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1))
+    pre_ms = sorted(times)[len(times) // 2]
+    out["prefill"] = {"batch": batch_prefill, "prompt": prompt, "ms": round(pre_ms, 3), "tok_per_s": round(batch_prefill * prompt / pre_ms * 1e3)}
+    out["prefill_kernels"] = _kernel_table(lambda: prefill(batch_prefill))
+    eng.release(range(batch_prefill))
+
+    # decode: batch_decode sequences at context `prompt`, one token each per step (second step captures the graph)
+    prefill(batch_decode)
+    nxt = [[int(t)] for t in torch.randint(0, cfg.vocab, (batch_decode,), generator=g)]
+    one = lambda: eng.feed([(i, nxt[i], [0]) for i in range(batch_decode)])  # noqa: E731
+    for _ in range(4):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(decode_steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    step_us = e0.elapsed_time(e1) * 1e3 / decode_steps
+    cap = next(iter(eng._graphs.values()), None)
+    dev_us = None
+    if cap is not None:   # device time of the replayed step alone (no host work between replays)
+        e0.record()
+        for _ in range(8):
+            cap.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        dev_us = e0.elapsed_time(e1) * 1e3 / 8
+        # (those replays re-ran the last step on the same rows: states moved, bookkeeping did not; the sequences end here)
+    n_params = sum(t.numel() for k, t in model_weights_bytes(model))
+    state_bytes = sum(v.states[n][0].numel() * 4 * 2 for layer in mgr.views for v in layer for n in v.states) * batch_decode
+    win = cfgd["layers"][3]["mixer"]["left"]
+    kv_bytes = sum(1 for L in cfgd["layers"] if L["type"] == "parallel") * batch_decode * (win["mask"]["size"] + win["mask"]["keep_first"]) * \
+        win["kv_heads"] * (win["dim"] + win["vdim"]) * 4
+    step_bytes = 2.0 * n_params + state_bytes + kv_bytes
+    out["decode"] = {"batch": batch_decode, "context": prompt, "us_per_step_engine": round(step_us, 1), "us_per_step_device": dev_us and round(dev_us, 1),
+                     "tok_per_s": round(batch_decode / step_us * 1e6), "step_algorithmic_MB": round(step_bytes / 1e6, 1),
+                     "hbm_frac_device": dev_us and round(step_bytes / (dev_us * 1e-6) / 1e9 / hbm, 3), "graph": cap is not None}
+    eng.use_graph = False   # per-kernel times from an eager step: under the graph's dependent launches a kernel's duration includes its wait
+    one()
+    out["decode_kernels_eager"] = _kernel_table(one)
+    eng.release(range(batch_decode))
+    del eng, mgr, model
+    torch.cuda.empty_cache()
+
+    # the closest existing model at equal width / depth / vocabulary: the RoPE GQA decoder with its static cache and decode graph
+    base = type("EqCfg", (DecodeCfg,), {"hidden_size": width, "num_attention_heads": width // 64, "num_hidden_layers": len(cfgd["layers"]),
+                                        "vocab_size": cfg.vocab, "max_position_embeddings": prompt + decode_steps + 8})
+    out["decoder_model_decode"] = _guarded(decode_config3, dev, "gqa", batch=batch_decode, prefill=prompt, new_tokens=decode_steps, base=base,
+                                           kv_heads=max(width // 256, 1), tag=f"decoder_clm_L{len(cfgd['layers'])}_w{width}")
+    out["decoder_model_prefill"] = _guarded(decode_config3, dev, "gqa", batch=batch_prefill, prefill=prompt, new_tokens=4, base=base,
+                                            kv_heads=max(width // 256, 1), tag=f"decoder_clm_L{len(cfgd['layers'])}_w{width}")
+    return out
+
+
+def model_weights_bytes(model):
+    """(name, tensor) of every weight a decode step reads (the embedding table is touched by one row per token)."""
+    seen = []
+    for L in model.layers:
+        seen.append(("inp", L.inp.weight))
+        for m in L.mixers:
+            for name in ("o", "a2", "g2"):
+                if hasattr(m, name):
+                    seen.append((name, getattr(m, name).weight))
+        if L.mlp is not None:
+            seen += [("up", L.mlp.up.weight), ("down", L.mlp.down.weight)]
+    seen.append(("head", model.head.weight))
+    return seen
+
+
+def run_hybrid(args):
+    from vyomai_b200 import _lib
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus != 1:
+        print(json.dumps({"workload": "hybrid", "error": "the hybrid decoder measurement runs on one GPU"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.vy_launch_count()
+    res = [_guarded(measure_hybrid, dev, int(w), steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3)) for w in args.hybrid_sizes.split(",")]
+    launches = L.vy_launch_count() - n0
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    print(json.dumps({"workload": "hybrid", "metric": "gelutar_prefill_and_decode_tokens_per_s", "n_gpus": 1, "dtype": "bf16 (fp32 residual / scores / state)",
+                      "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
+                      "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -909,9 +1071,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="package", choices=["package", "slots"],
-                    help="package: VisionLanguageModel of the reference package (1 image token + 127 text, the headline since round 1); "
-                         "slots: the notebook-II form (197 image tokens in a 248-token sequence)")
+    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid"],
+                    help="package: VisionLanguageModel of the reference package (1 image token + 127 text, the headline); "
+                         "slots: the notebook-II form (197 image tokens in a 248-token sequence); "
+                         "hybrid: prefill / decode throughput of the Gelutar hybrid decoder beside DecoderModel at equal size (1 GPU, "
+                         "its own JSON line; not the headline metric)")
+    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid: model widths to measure")
     ap.add_argument("--no-configs-1-2", action="store_true", help="skip the encoder (C1) / ViT (C2) measurements appended at N = 1")
     ap.add_argument("--no-config5", action="store_true", help="skip the PaliGemma-scale prefill + decode measurement appended at N = 1")
     ap.add_argument("--no-slots", action="store_true", help="skip the notebook-II measurement appended at N = 1")
@@ -926,6 +1091,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "hybrid":
+        run_hybrid(args)
     else:
         run_ours(args)
 

@@ -69,16 +69,13 @@ class GelutarConfig:
                             q + "q.norm": (a["heads"] * a["dim"],), q + "k.norm": (a["kv_heads"] * a["dim"],), q + "sink": (a["heads"],),
                             q + "g": (a["heads"], W), q + "o": (W, a["heads"] * a["vdim"]), q + "out": (W,)})
                 q = p + "mix.right."
-                rank_a = r.get("rank_a", r.get("rank", None))
                 out.update({q + "q": (r["kv_heads"] * r["dim"], W), q + "k": (r["kv_heads"] * r["dim"], W), q + "v": (r["heads"] * r["vdim"], W),
                             q + "q.conv": (r["kv_heads"] * r["dim"], r["conv"]), q + "k.conv": (r["kv_heads"] * r["dim"], r["conv"]),
                             q + "v.conv": (r["heads"] * r["vdim"], r["conv"]), q + "b": (r["heads"], W), q + "A_log": (r["heads"],),
                             q + "norm": (r["vdim"],), q + "dt_bias": (r["heads"] * r["dim"],), q + "o": (W, r["heads"] * r["vdim"]),
                             q + "out": (W,)})
-                out[q + "a1"] = (rank_a, W) if rank_a else None   # the low ranks are read off the checkpoint
-                out[q + "a2"] = (r["heads"] * r["dim"], rank_a) if rank_a else None
-                out[q + "g1"] = out[q + "a1"]
-                out[q + "g2"] = (r["heads"] * r["vdim"], rank_a) if rank_a else None
+                # the two low ranks are not configuration: -1 stands for "whatever the checkpoint holds", and the pairs must agree
+                out.update({q + "a1": (-1, W), q + "a2": (r["heads"] * r["dim"], -1), q + "g1": (-1, W), q + "g2": (r["heads"] * r["vdim"], -1)})
             if L.get("mlp"):
                 out.update({p + "norm2": (W,), p + "mlp.up": (L["mlp"]["ff"], W), p + "mlp.down": (W, L["mlp"]["ff"])})
         return out
@@ -149,8 +146,11 @@ class GelutarForCausalLM:
         if missing:
             raise KeyError(f"checkpoint lacks {missing[:5]}{' ...' if len(missing) > 5 else ''}")
         for k, shp in need.items():
-            if shp is not None and tuple(weights[k].shape) != tuple(shp):
-                raise ValueError(f"{k}: shape {tuple(weights[k].shape)}, the configuration implies {tuple(shp)}")
+            got = tuple(weights[k].shape)
+            if len(got) != len(shp) or any(a != b for a, b in zip(got, shp) if b >= 0):
+                raise ValueError(f"{k}: shape {got}, the configuration implies {tuple(shp)}")
+            if k.endswith(("mix.right.a1", "mix.right.g1")) and weights[k[:-1] + "2"].shape[1] != got[0]:
+                raise ValueError(f"{k}: rank {got[0]} does not match {k[:-1]}2")
         w = {k: v.to(device=self.device, dtype=dtype) for k, v in weights.items() if k in need}
         self.embed = w["embed"].contiguous()
         self.final_norm = w["final.norm"].contiguous()
@@ -164,19 +164,18 @@ class GelutarForCausalLM:
         return cls(GelutarConfig.from_dir(path), load_safetensors(os.path.join(path, "model.safetensors")), dtype=dtype, device=device, **kw)
 
     @staticmethod
-    def random_weights(config: GelutarConfig, seed: int = 0, low_rank: int = 16) -> Dict[str, torch.Tensor]:
+    def random_weights(config: GelutarConfig, seed: int = 0, low_rank=16) -> Dict[str, torch.Tensor]:
         """Seeded bf16 weights of the right shapes (tests, benchmarks): projections ~ N(0, 1/in), norm weights and sinks small,
-        A_log and dt_bias in the range that gives decays between ~0.5 and ~1."""
+        A_log and dt_bias in the range that gives decays between ~0.5 and ~1. `low_rank`: one rank, or (decay rank, gate rank)
+        of the delta mixer's two factored projections."""
         g = torch.Generator().manual_seed(seed)
+        ranks = (low_rank, low_rank) if isinstance(low_rank, int) else tuple(low_rank)
         out = {}
         for k, shp in config.tensor_shapes().items():
             leaf = k.split(".")[-1]
-            if shp is None:
-                base = k[: -len(leaf)]
-                r = config.layers[int(k[1:k.index(".")])]["mixer"]["right"]
-                W = config.width
-                shp = {"a1": (low_rank, W), "g1": (low_rank, W), "a2": (r["heads"] * r["dim"], low_rank),
-                       "g2": (r["heads"] * r["vdim"], low_rank)}[leaf]
+            if -1 in shp:
+                rank = ranks[0] if leaf in ("a1", "a2") else ranks[1]
+                shp = tuple(rank if n < 0 else n for n in shp)
             if len(shp) == 2 and leaf != "conv":
                 t = torch.randn(shp, generator=g) / (shp[1] ** 0.5)
                 if leaf == "embed":

@@ -1,4 +1,4 @@
-"""Paged kv-cache and continuous batching for the decoder family (SURVEY.md §8f item 3).
+"""Paged kv-cache and continuous batching for the decoder family.
 
 Host-side mirror of `Examples/simple_vllm.ipynb` cell 2 of the reference — `SequenceState`, `PagedKVManager`
 (`can_allocate` / `allocate` / `free`, pools of shape (max_blocks, block_size, kv_heads, head_dim) per layer) and
@@ -228,6 +228,7 @@ class HybridCacheManager:
         self.views: List[List[LayerCacheView]] = [[LayerCacheView() for _ in layer] for layer in self._specs]
         self.num_blocks = 0
         self.num_slots = 0
+        self.generation = 0
         self.free_blocks: deque = deque()
         self.free_slots: deque = deque()
         self._grow_slots(max(1, int(max_seqs)))
@@ -250,6 +251,7 @@ class HybridCacheManager:
                     setattr(view, name, new)
         self.free_blocks.extend(range(self.num_blocks, new_total))
         self.num_blocks = new_total
+        self.generation += 1   # pool tensors were replaced: captured steps that point at the old ones are stale
 
     def _grow_slots(self, n_more: int) -> None:
         new_total = self.num_slots + n_more
@@ -262,6 +264,7 @@ class HybridCacheManager:
                     view.states[name] = new
         self.free_slots.extend(range(self.num_slots, new_total))
         self.num_slots = new_total
+        self.generation += 1
 
     def blocks_for(self, n_tokens: int) -> int:
         return (n_tokens + self.block_size - 1) // self.block_size if self.has_pages else 0
@@ -291,6 +294,42 @@ class HybridCacheManager:
         seq.num_cached = 0
 
 
+class _CapturedStep:
+    """One single-token step of `n` sequences with a block table `width` pages wide, captured into a CUDA graph. The step's
+    integers (token rows, positions, slots, block table, ids) live in one static device buffer that every replay refreshes
+    from pinned host memory; the logits of all n rows come back in a static tensor. Capturing runs nothing, so the states
+    and pages advance only on replay. Valid for the pool tensors of the manager generation it was captured under."""
+
+    def __init__(self, engine: "HybridBatchEngine", n: int, width: int):
+        import os
+        from . import _lib
+        self.n = n
+        _, total = engine._layout(n, width, n, n)
+        self.flat = torch.zeros(total, dtype=torch.int32, device=engine.device)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.copied = None
+        batch, ids_t, rows_t = engine._views(self.flat, n, width, n, n, 1)
+        self.graph = torch.cuda.CUDAGraph()
+        pdl = os.environ.get("VY_DECODE_PDL", "1") != "0"   # each short kernel's launch overlaps its predecessor's tail
+        prev = _lib.lib().vy_set_pdl(1) if pdl else None
+        try:
+            with torch.cuda.graph(self.graph), torch.no_grad():
+                self.logits = engine.model.step(ids_t, batch, engine.cache.views, rows_t)
+        finally:
+            if pdl:
+                _lib.lib().vy_set_pdl(prev)
+
+    def replay(self, host_ints: torch.Tensor) -> torch.Tensor:
+        if self.copied is not None:
+            self.copied.synchronize()   # the previous replay's upload has left the pinned buffer
+        self.host.copy_(host_ints)
+        self.flat.copy_(self.host, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        self.graph.replay()
+        return self.logits
+
+
 class HybridBatchEngine:
     """Continuous batching for hybrid models, the counterpart of ContinuousBatchEngine for models with a packed `step`
     (models/gelutar.py): every engine iteration is ONE model step over the concatenated new tokens of all live
@@ -299,7 +338,8 @@ class HybridBatchEngine:
     length retirement as above); `feed()` / `release()` advance named sequences by GIVEN tokens and return the logits of
     chosen rows (replaying a recorded trace, scoring, teacher forcing) through the same step and manager."""
 
-    def __init__(self, model, cache_mgr: HybridCacheManager, max_batch_size: int = 16, eos_token_ids: Iterable[int] = ()):
+    def __init__(self, model, cache_mgr: HybridCacheManager, max_batch_size: int = 16, eos_token_ids: Iterable[int] = (),
+                 use_graph: bool = True):
         self.model, self.cache = model, cache_mgr
         self.device = cache_mgr.device
         self.max_batch = max_batch_size
@@ -307,8 +347,29 @@ class HybridBatchEngine:
         self.active: Dict[object, HybridSequence] = {}
         self.waiting_room: deque = deque()
         self.id_gen = itertools.count()
+        # single-token steps are a chain of short kernels whose arguments all live in device arrays: the second time a
+        # (batch size, table width) shape comes up it is captured into a CUDA graph and replayed from then on
+        self.use_graph = bool(use_graph) and self.device.type == "cuda"
+        self._graphs: Dict[tuple, "_CapturedStep"] = {}
+        self._seen: Dict[tuple, int] = {}
 
     # ---- the shared step ----
+    @staticmethod
+    def _layout(n: int, width: int, n_ids: int, n_rows: int):
+        """Offsets of cu_tokens | pos0 | slot | block table | ids | wanted rows inside the step's one int32 staging buffer."""
+        sizes = (n + 1, n, n, n * width, n_ids, n_rows)
+        offs, at = [], 0
+        for k in sizes:
+            offs.append((at, k))
+            at += k
+        return offs, at
+
+    def _views(self, flat: torch.Tensor, n: int, width: int, n_ids: int, n_rows: int, max_new: int):
+        offs, _ = self._layout(n, width, n_ids, n_rows)
+        cu_t, pos_t, slot_t, table_t, ids_t, rows_t = (flat[o:o + k] for o, k in offs)
+        batch = ops.PackedBatch(cu_t, pos_t, slot_t, max_new, table_t.view(n, width) if self.cache.has_pages else None, self.cache.block_size)
+        return batch, ids_t, rows_t
+
     @torch.no_grad()
     def _run(self, work: List, want: List[List[int]]) -> torch.Tensor:
         """work: [(sequence, new tokens)]; want[i]: offsets among sequence i's new tokens whose logits are returned
@@ -328,25 +389,39 @@ class HybridBatchEngine:
             slot.append(seq.slot)
             ids += [int(t) for t in toks]
             cu.append(cu[-1] + len(toks))
+        max_new = max(len(t) for _, t in work)
         width = max(1, max(len(seq.blocks) for seq, _ in work))
+        single = max_new == 1 and self.use_graph
+        if single:   # few distinct table widths, so few captures
+            width = max(8, 1 << (width - 1).bit_length())
         table = []
         for seq, _ in work:
             table += seq.blocks + [0] * (width - len(seq.blocks))
-        flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32)
-        if self.device.type == "cuda":   # one pinned staging buffer, one host-to-device copy per step
-            flat = flat.pin_memory().to(self.device, non_blocking=True)
-        o = 0
-
-        def take(k):
-            nonlocal o
-            t = flat[o:o + k]
-            o += k
-            return t
-        cu_t, pos_t, slot_t = take(n + 1), take(n), take(n)
-        table_t = take(n * width).view(n, width)
-        ids_t, rows_t = take(len(ids)), take(len(rows))
-        batch = ops.PackedBatch(cu_t, pos_t, slot_t, max(len(t) for _, t in work), table_t if mgr.has_pages else None, mgr.block_size)
-        logits = self.model.step(ids_t, batch, mgr.views, rows_t if rows else None)
+        if single:
+            host = torch.tensor(cu + pos0 + slot + table + ids + list(range(n)), dtype=torch.int32)
+            key = (n, width, mgr.generation)
+            if self._graphs and next(iter(self._graphs))[2] != mgr.generation:
+                self._graphs.clear()   # the pools were re-allocated: those captures point at freed tensors
+            cap = self._graphs.get(key)
+            if cap is None and self._seen.get(key, 0) >= 1:
+                if len(self._graphs) >= 32:
+                    self._graphs.clear()
+                cap = self._graphs[key] = _CapturedStep(self, n, width)
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if cap is not None:
+                all_rows = cap.replay(host)
+                logits = all_rows[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else None
+            else:
+                flat = host.pin_memory().to(self.device, non_blocking=True)
+                batch, ids_t, rows_t = self._views(flat, n, width, n, n, 1)
+                all_rows = self.model.step(ids_t, batch, mgr.views, rows_t)
+                logits = all_rows[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else None
+        else:
+            flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32)
+            if self.device.type == "cuda":   # one pinned staging buffer, one host-to-device copy per step
+                flat = flat.pin_memory().to(self.device, non_blocking=True)
+            batch, ids_t, rows_t = self._views(flat, n, width, len(ids), len(rows), max_new)
+            logits = self.model.step(ids_t, batch, mgr.views, rows_t if rows else None)
         for seq, toks in work:
             seq.num_cached += len(toks)
         return logits
