@@ -6,31 +6,9 @@
 // a sequence sits in the batch.
 #include <math.h>
 
-#include "vy_common.cuh"
+#include "seqmix.cuh"
 
 namespace vy {
-
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
-__device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
-__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
-__device__ __forceinline__ float apply_uact(float x, int act) {
-  switch (act) {
-    case VY_UACT_RELU2: { const float r = fmaxf(x, 0.f); return r * r; }
-    case VY_UACT_SILU: return siluf_(x);
-    case VY_UACT_SIGMOID: return sigmoidf_(x);
-    default: return x;
-  }
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
 
 // ---- RMS norm -------------------------------------------------------------------------------------------------------
 struct NormDev {
@@ -75,6 +53,58 @@ __global__ void __launch_bounds__(128) rms_norm_kernel(NormDev d) {
   }
 }
 
+// The same with the row held in registers (one read of x) and TPR threads per row, 256 threads per CTA: for widths up to
+// 8 TPR. Few wide rows (single-token steps) get many threads each; many narrow rows get a warp each.
+template <int TPR>
+__global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int NC = 8, RPB = 256 / TPR;
+  __shared__ float part[RPB][TPR / 32 + 1];
+  const int lr = threadIdx.x / TPR, lt = threadIdx.x % TPR;
+  const long long r = blockIdx.x * static_cast<long long>(RPB) + lr;
+  const bool live = r < d.rows;
+  const long long tok = live ? r / d.groups : 0;
+  const int grp = live ? static_cast<int>(r - tok * d.groups) : 0;
+  const long long st = d.row_index ? d.row_index[tok] : tok;
+  const long long xo = st * d.ldx + static_cast<long long>(grp) * d.width;
+  float xv[NC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int c = lt + i * TPR;
+    xv[i] = (live && c < d.width) ? ld_as_float(d.x, d.x_dt, xo + c) : 0.f;
+    ss = fmaf(xv[i], xv[i], ss);
+  }
+  ss = warp_sum(ss);
+  if (TPR > 32) {
+    if ((threadIdx.x & 31) == 0) part[lr][lt >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < TPR / 32; ++w) ss += part[lr][w];
+  }
+  if (!live) return;
+  const float inv = d.coef / sqrtf(ss / static_cast<float>(d.width) + d.eps);
+  const long long go = st * d.ld_gate + static_cast<long long>(grp) * d.width;
+  const long long oo = tok * d.ld_out + static_cast<long long>(grp) * d.width;
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int c = lt + i * TPR;
+    if (c < d.width) {
+      float y = xv[i] * inv;
+      if (d.w_mode == 1) y *= ld_as_float(d.w, d.w_dt, c);
+      else if (d.w_mode == 2) y *= 1.f + ld_as_float(d.w, d.w_dt, c);
+      if (d.gate) {
+        const float g = ld_as_float(d.gate, d.gate_dt, go + c);
+        y *= d.gate_act == VY_UACT_SIGMOID ? sigmoidf_(g) : g;
+      }
+      if (d.accumulate) y += ld_as_float(d.out, d.out_dt, oo + c);
+      st_from_float(d.out, d.out_dt, oo + c, y);
+    }
+  }
+}
+
 // ---- paged key / value write ------------------------------------------------------------------------------------------
 struct KvwDev {
   const int* cu; const int* pos0; const int* table; int tw, bs;
@@ -100,19 +130,11 @@ __global__ void __launch_bounds__(128) kv_page_write_kernel(KvwDev d) {
 }
 
 // ---- windowed attention with kept first tokens and a sink ---------------------------------------------------------------
-struct WinDev {
-  const int* cu; const int* pos0; const int* table; int tw, bs;
-  const void* q; long long ldq; int q_dt;
-  const void* kp; const void* vp; int pool_dt;
-  int heads, kv_heads, dim, vdim;
-  float scale; int window, keep;
-  const void* sink; int sink_dt;
-  const void* gate; long long ld_gate; int gate_dt;
-  void* out; long long ld_out; int out_dt;
-};
 
 constexpr int WA_WARPS = 4;
 constexpr int WA_VR = 8;  // value columns per lane: vdim <= 256
+constexpr int WA_TILED_MIN = 16;   // longest portion of a step from which the tiled prompt kernel (seqmix_tiled.cu) takes over
+constexpr int LA_CHUNKED_MIN = 8;  // same for the chunked linear attention
 
 __device__ __forceinline__ float dot_row(const void* base, int dt, long long off, int n, const float* __restrict__ qs) {
   float acc = 0.f;
@@ -138,7 +160,7 @@ __device__ __forceinline__ float dot_row(const void* base, int dt, long long off
   return acc;
 }
 
-template <bool SPLIT>
+// portions of a few tokens: one warp per query, lanes over 32 keys at a time
 __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
   pdl_trigger();
   pdl_wait();
@@ -146,8 +168,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
   const int s = blockIdx.z, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
-  const int qi = SPLIT ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * WA_WARPS + warp;
-  if (qi >= n) return;  // SPLIT: uniform over the CTA; otherwise the warps never meet at a CTA barrier
+  const int qi = static_cast<int>(blockIdx.x) * WA_WARPS + warp;
+  if (qi >= n) return;  // the warps never meet at a CTA barrier
   const int g = h / (d.heads / d.kv_heads);
   float* qs = wa_smem + warp * d.dim;
   const long long qrow = base + qi;
@@ -159,7 +181,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
   const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
   const int count = nA + (pos + 1 - lowB);
   float m = -INFINITY, l = 0.f;
-  if (d.sink && (!SPLIT || warp == 0)) {
+  if (d.sink) {
     m = ld_as_float(d.sink, d.sink_dt, h);
     l = 1.f;
   }
@@ -169,7 +191,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
   const int kstride = d.kv_heads * d.dim, vstride = d.kv_heads * d.vdim;
   const int tiles = (count + 31) >> 5;
-  for (int tt = SPLIT ? warp : 0; tt < tiles; tt += SPLIT ? WA_WARPS : 1) {
+  for (int tt = 0; tt < tiles; ++tt) {
     const int c = tt * 32 + lane;
     const bool valid = c < count;
     long long row = 0;
@@ -198,42 +220,131 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
       }
     }
   }
-  if (SPLIT) {
-    // merge the four partial softmaxes in warp order
-    float* ms = wa_smem + WA_WARPS * d.dim;       // [WA_WARPS]
-    float* ls = ms + WA_WARPS;                    // [WA_WARPS]
-    float* as = ls + WA_WARPS;                    // [WA_WARPS][vdim]
-    if (lane == 0) { ms[warp] = m; ls[warp] = l; }
-#pragma unroll
-    for (int r = 0; r < WA_VR; ++r) {
-      const int col = lane + 32 * r;
-      if (col < d.vdim) as[warp * d.vdim + col] = acc[r];
-    }
-    __syncthreads();
-    if (warp != 0) return;
-    float M = ms[0];
-    for (int w = 1; w < WA_WARPS; ++w) M = fmaxf(M, ms[w]);
-    l = 0.f;
-    float wgt[WA_WARPS];
-    for (int w = 0; w < WA_WARPS; ++w) {
-      wgt[w] = ms[w] == -INFINITY ? 0.f : expf(ms[w] - M);
-      l += ls[w] * wgt[w];
-    }
-#pragma unroll
-    for (int r = 0; r < WA_VR; ++r) {
-      const int col = lane + 32 * r;
-      float a = 0.f;
-      if (col < d.vdim)
-        for (int w = 0; w < WA_WARPS; ++w) a += as[w * d.vdim + col] * wgt[w];
-      acc[r] = a;
-    }
-  }
   float og = 1.f / l;
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
     const int col = lane + 32 * r;
     if (col < d.vdim) st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, acc[r] * og);
+  }
+}
+
+// single tokens: one CTA per (head, sequence); its warps take the visible keys four at a time, round-robin, each lane holding
+// every 32nd channel of the query and of the output (coalesced key / value rows), and the warps' partial softmaxes are merged
+// in warp order at the end
+constexpr int WD_WARPS = 8;
+constexpr int WD_KEYS = 4;
+
+__global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDev d) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float wa_smem[];
+  const int s = blockIdx.z, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int base = d.cu[s];
+  if (d.cu[s + 1] - base <= 0) return;
+  const int g = h / (d.heads / d.kv_heads);
+  const long long qrow = base;
+  float qreg[WA_VR];
+#pragma unroll
+  for (int r = 0; r < WA_VR; ++r) {
+    const int col = lane + 32 * r;
+    qreg[r] = col < d.dim ? ld_as_float(d.q, d.q_dt, qrow * d.ldq + static_cast<long long>(h) * d.dim + col) * d.scale : 0.f;
+  }
+  const int pos = d.pos0[s];
+  const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
+  const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
+  const int count = nA + (pos + 1 - lowB);
+  float m = -INFINITY, l = 0.f;
+  if (d.sink && warp == 0) {
+    m = ld_as_float(d.sink, d.sink_dt, h);
+    l = 1.f;
+  }
+  float acc[WA_VR];
+#pragma unroll
+  for (int r = 0; r < WA_VR; ++r) acc[r] = 0.f;
+  const int* tab = d.table + static_cast<long long>(s) * d.tw;
+  const long long kstride = static_cast<long long>(d.kv_heads) * d.dim, vstride = static_cast<long long>(d.kv_heads) * d.vdim;
+  for (int c0 = WD_KEYS * warp; c0 < count; c0 += WD_KEYS * WD_WARPS) {
+    long long row[WD_KEYS];
+    float sc[WD_KEYS], vv[WD_KEYS][WA_VR];
+#pragma unroll
+    for (int u = 0; u < WD_KEYS; ++u) {
+      const int c = min(c0 + u, count - 1);   // past the end: a repeat of the last key, given weight 0 below
+      const int kp = c < nA ? c : lowB + (c - nA);
+      row[u] = static_cast<long long>(tab[kp / d.bs]) * d.bs + kp % d.bs;
+      sc[u] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < WA_VR; ++r) {
+      const int col = lane + 32 * r;
+      if (col < d.dim) {
+#pragma unroll
+        for (int u = 0; u < WD_KEYS; ++u)
+          sc[u] = fmaf(qreg[r], ld_as_float(d.kp, d.pool_dt, row[u] * kstride + static_cast<long long>(g) * d.dim + col), sc[u]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < WA_VR; ++r) {
+      const int col = lane + 32 * r;
+#pragma unroll
+      for (int u = 0; u < WD_KEYS; ++u)
+        vv[u][r] = col < d.vdim ? ld_as_float(d.vp, d.pool_dt, row[u] * vstride + static_cast<long long>(g) * d.vdim + col) : 0.f;
+    }
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < WD_KEYS; ++u) {
+      sc[u] = c0 + u < count ? warp_sum(sc[u]) : -INFINITY;
+      m_new = fmaxf(m_new, sc[u]);
+    }
+    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+    float p[WD_KEYS], ps = 0.f;
+#pragma unroll
+    for (int u = 0; u < WD_KEYS; ++u) {
+      p[u] = c0 + u < count ? expf(sc[u] - m_new) : 0.f;
+      ps += p[u];
+    }
+    l = fmaf(l, corr, ps);
+    m = m_new;
+#pragma unroll
+    for (int r = 0; r < WA_VR; ++r) {
+      float a = acc[r] * corr;
+#pragma unroll
+      for (int u = 0; u < WD_KEYS; ++u) a = fmaf(p[u], vv[u][r], a);
+      acc[r] = a;
+    }
+  }
+  float* ms = wa_smem;                          // [WD_WARPS]
+  float* ls = ms + WD_WARPS;                    // [WD_WARPS]
+  float* as = ls + WD_WARPS;                    // [WD_WARPS][vdim]
+  if (lane == 0) { ms[warp] = m; ls[warp] = l; }
+#pragma unroll
+  for (int r = 0; r < WA_VR; ++r) {
+    const int col = lane + 32 * r;
+    if (col < d.vdim) as[warp * d.vdim + col] = acc[r];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float M = ms[0];
+  for (int w = 1; w < WD_WARPS; ++w) M = fmaxf(M, ms[w]);
+  l = 0.f;
+  float wgt[WD_WARPS];
+#pragma unroll
+  for (int w = 0; w < WD_WARPS; ++w) {
+    wgt[w] = ms[w] == -INFINITY ? 0.f : expf(ms[w] - M);
+    l = fmaf(ls[w], wgt[w], l);
+  }
+  float og = 1.f / l;
+  if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
+#pragma unroll
+  for (int r = 0; r < WA_VR; ++r) {
+    const int col = lane + 32 * r;
+    if (col < d.vdim) {
+      float a = 0.f;
+#pragma unroll
+      for (int w = 0; w < WD_WARPS; ++w) a = fmaf(as[w * d.vdim + col], wgt[w], a);
+      st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, a * og);
+    }
   }
 }
 
@@ -301,18 +412,6 @@ __global__ void __launch_bounds__(128) causal_conv_state_kernel(ConvDev d) {
 }
 
 // ---- recurrences: one thread owns one column of the dim x vdim state in registers ---------------------------------------
-struct RecDev {
-  const int* cu; const int* pos0; const int* slot;
-  const void* q; long long ldq; const void* k; long long ldk; const void* v; long long ldv; int in_dt; int in_act;
-  const void* a; long long ld_a; int a_dt;
-  const void* b; long long ld_b; int b_dt;
-  const void* a_log; int a_log_dt;
-  const float* decay;
-  int heads, kv_heads, dim, vdim;
-  float unit_eps;
-  float* state;
-  void* out; long long ld_out; int out_dt;
-};
 
 template <int DP>
 struct RecChunk { static constexpr int CT = DP >= 256 ? 8 : 16; };
@@ -372,19 +471,23 @@ __global__ void __launch_bounds__(128) linear_attn_kernel(RecDev d) {
   }
 }
 
-// gated delta rule
+// gated delta rule: a column of the state is shared by 4 adjacent lanes, lane `part` holding channels 16 m + 4 part .. + 3 of
+// every group of 16 (so the chunk's k / q / decay rows are read as one float4 per group and a warp touches 64 contiguous bytes);
+// the two contractions over the channels end in two shuffles each
 template <int DP>
 __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
   pdl_trigger();
   pdl_wait();
   constexpr int CT = RecChunk<DP>::CT;
-  extern __shared__ float dr_smem[];
+  constexpr int NM = DP / 16;
+  extern __shared__ __align__(16) float dr_smem[];
   float (*qs)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem);
   float (*ks)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem + CT * DP);
   float (*gs)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem + 2 * CT * DP);
   float* betas = dr_smem + 3 * CT * DP;
   const int s = blockIdx.z, h = blockIdx.y;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x & 3;
+  const int j = blockIdx.x * 32 + (threadIdx.x >> 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
   if (n <= 0) return;
@@ -392,29 +495,50 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
   const int gq = h / (d.heads / d.kv_heads);
   const float neg_rate = -expf(ld_as_float(d.a_log, d.a_log_dt, h));
   const float qscale = 1.f / sqrtf(static_cast<float>(d.dim));
-  float S[DP];
+  float S[NM][4];
   float* sp = d.state + ((static_cast<long long>(d.slot[s]) * d.heads + h) * d.dim) * d.vdim + j;
   const bool carried = d.pos0[s] > 0;
 #pragma unroll
-  for (int i = 0; i < DP; ++i) S[i] = (carried && active && i < d.dim) ? sp[static_cast<long long>(i) * d.vdim] : 0.f;
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * m + 4 * part + e;
+      S[m][e] = (carried && active && i < d.dim) ? sp[static_cast<long long>(i) * d.vdim] : 0.f;
+    }
+  // the next chunk's raw q / k / decay inputs travel in registers while the current chunk is walked
+  constexpr int NPF = CT * DP / 128;
+  float rq[NPF], rk[NPF], ra[NPF], rb = 0.f;
+  auto fetch = [&](int t0) {
+    const int nt = min(CT, n - t0);
+#pragma unroll
+    for (int u = 0; u < NPF; ++u) {
+      const int e = threadIdx.x + u * 128, tt = e / DP, i = e - tt * DP;
+      const bool ok = tt < nt && i < d.dim;
+      const long long row = base + t0 + tt;
+      rq[u] = ok ? ld_as_float(d.q, d.in_dt, row * d.ldq + static_cast<long long>(gq) * d.dim + i) : 0.f;
+      rk[u] = ok ? ld_as_float(d.k, d.in_dt, row * d.ldk + static_cast<long long>(gq) * d.dim + i) : 0.f;
+      ra[u] = ok ? ld_as_float(d.a, d.a_dt, row * d.ld_a + static_cast<long long>(h) * d.dim + i) : -INFINITY;
+    }
+    if (threadIdx.x < nt) rb = ld_as_float(d.b, d.b_dt, static_cast<long long>(base + t0 + threadIdx.x) * d.ld_b + h);
+  };
+  fetch(0);
   for (int t0 = 0; t0 < n; t0 += CT) {
     const int nt = min(CT, n - t0);
     __syncthreads();
+#pragma unroll
+    for (int u = 0; u < NPF; ++u) {
+      const int e = threadIdx.x + u * 128, tt = e / DP, i = e - tt * DP;
+      qs[tt][i] = rq[u];
+      ks[tt][i] = rk[u];
+      gs[tt][i] = ra[u] == -INFINITY ? 1.f : expf(neg_rate * softplusf_(ra[u]));
+    }
+    if (threadIdx.x < nt) betas[threadIdx.x] = sigmoidf_(rb);
+    __syncthreads();
     for (int tt = warp; tt < nt; tt += nwarps) {
-      const long long row = base + t0 + tt;
       float sq = 0.f, sk = 0.f;
       for (int i = lane; i < DP; i += 32) {
-        float qv = 0.f, kv = 0.f, gv = 1.f;
-        if (i < d.dim) {
-          qv = ld_as_float(d.q, d.in_dt, row * d.ldq + static_cast<long long>(gq) * d.dim + i);
-          kv = ld_as_float(d.k, d.in_dt, row * d.ldk + static_cast<long long>(gq) * d.dim + i);
-          gv = expf(neg_rate * softplusf_(ld_as_float(d.a, d.a_dt, row * d.ld_a + static_cast<long long>(h) * d.dim + i)));
-        }
-        sq = fmaf(qv, qv, sq);
-        sk = fmaf(kv, kv, sk);
-        qs[tt][i] = qv;
-        ks[tt][i] = kv;
-        gs[tt][i] = gv;
+        sq = fmaf(qs[tt][i], qs[tt][i], sq);
+        sk = fmaf(ks[tt][i], ks[tt][i], sk);
       }
       sq = warp_sum(sq);
       sk = warp_sum(sk);
@@ -423,34 +547,55 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
         qs[tt][i] *= qn;
         ks[tt][i] *= kn;
       }
-      if (lane == 0) betas[tt] = sigmoidf_(ld_as_float(d.b, d.b_dt, row * d.ld_b + h));
     }
     __syncthreads();
-    if (active) {
-      for (int tt = 0; tt < nt; ++tt) {
-        const long long row = base + t0 + tt;
-        const float vj = ld_as_float(d.v, d.in_dt, row * d.ldv + static_cast<long long>(h) * d.vdim + j);
-        float r = 0.f;
+    if (t0 + CT < n) fetch(t0 + CT);
+    for (int tt = 0; tt < nt; ++tt) {
+      const long long row = base + t0 + tt;
+      const float vj = active ? ld_as_float(d.v, d.in_dt, row * d.ldv + static_cast<long long>(h) * d.vdim + j) : 0.f;
+      float4 k4[NM];
+      float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-          S[i] *= gs[tt][i];
-          r = fmaf(S[i], ks[tt][i], r);
-        }
-        const float u = betas[tt] * (vj - r);
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-          S[i] = fmaf(ks[tt][i], u, S[i]);
-          o = fmaf(S[i], qs[tt][i], o);
-        }
-        st_from_float(d.out, d.out_dt, row * d.ld_out + static_cast<long long>(h) * d.vdim + j, o);
+      for (int m = 0; m < NM; ++m) {
+        const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][16 * m + 4 * part]);
+        k4[m] = *reinterpret_cast<const float4*>(&ks[tt][16 * m + 4 * part]);
+        S[m][0] *= g4.x; S[m][1] *= g4.y; S[m][2] *= g4.z; S[m][3] *= g4.w;
+        r0 = fmaf(S[m][0], k4[m].x, r0);
+        r1 = fmaf(S[m][1], k4[m].y, r1);
+        r0 = fmaf(S[m][2], k4[m].z, r0);
+        r1 = fmaf(S[m][3], k4[m].w, r1);
       }
+      float r = r0 + r1;
+      r += __shfl_xor_sync(0xffffffffu, r, 1);
+      r += __shfl_xor_sync(0xffffffffu, r, 2);
+      const float u = betas[tt] * (vj - r);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int m = 0; m < NM; ++m) {
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][16 * m + 4 * part]);
+        S[m][0] = fmaf(k4[m].x, u, S[m][0]);
+        S[m][1] = fmaf(k4[m].y, u, S[m][1]);
+        S[m][2] = fmaf(k4[m].z, u, S[m][2]);
+        S[m][3] = fmaf(k4[m].w, u, S[m][3]);
+        o0 = fmaf(S[m][0], q4.x, o0);
+        o1 = fmaf(S[m][1], q4.y, o1);
+        o0 = fmaf(S[m][2], q4.z, o0);
+        o1 = fmaf(S[m][3], q4.w, o1);
+      }
+      float o = o0 + o1;
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (active && part == 0) st_from_float(d.out, d.out_dt, row * d.ld_out + static_cast<long long>(h) * d.vdim + j, o);
     }
   }
   if (active) {
 #pragma unroll
-    for (int i = 0; i < DP; ++i)
-      if (i < d.dim) sp[static_cast<long long>(i) * d.vdim] = S[i];
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 16 * m + 4 * part + e;
+        if (i < d.dim) sp[static_cast<long long>(i) * d.vdim] = S[m][e];
+      }
   }
 }
 
@@ -481,9 +626,15 @@ extern "C" int vy_rms_norm(const VyRmsNorm* p) {
   d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype; d.gate_act = p->gate_act;
   d.eps = p->eps; d.coef = p->coef == 0.f ? 1.f : p->coef; d.accumulate = p->accumulate;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
-  const long long blocks = (d.rows + 3) / 4;
+  cudaStream_t st = static_cast<cudaStream_t>(p->stream);
+  const int tpr = d.width <= 256 ? 32 : d.width <= 1024 ? 128 : d.width <= 2048 ? 256 : 0;
+  const long long blocks = tpr ? (d.rows + 256 / tpr - 1) / (256 / tpr) : (d.rows + 3) / 4;
   VY_CHECK_ARG(blocks <= 2147483647LL, "vy_rms_norm: too many rows");
-  VY_CUDA_OK(launch_kernel(rms_norm_kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 0, static_cast<cudaStream_t>(p->stream), d));
+  const dim3 grid(static_cast<unsigned>(blocks));
+  if (tpr == 32) VY_CUDA_OK(launch_kernel(rms_norm_cached_kernel<32>, grid, dim3(256), 0, st, d));
+  else if (tpr == 128) VY_CUDA_OK(launch_kernel(rms_norm_cached_kernel<128>, grid, dim3(256), 0, st, d));
+  else if (tpr == 256) VY_CUDA_OK(launch_kernel(rms_norm_cached_kernel<256>, grid, dim3(256), 0, st, d));
+  else VY_CUDA_OK(launch_kernel(rms_norm_kernel, grid, dim3(128), 0, st, d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;
@@ -533,13 +684,16 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
   d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
-  const size_t smem = sizeof(float) * (static_cast<size_t>(WA_WARPS) * p->dim + 2 * WA_WARPS + static_cast<size_t>(WA_WARPS) * p->vdim);
-  VY_CHECK_ARG(smem <= 48 * 1024, "vy_window_attn: dim %d too large", p->dim);
-  if (p->max_new == 1) {
-    VY_CUDA_OK(launch_kernel(window_attn_kernel<true>, dim3(1, p->heads, p->n_seqs), dim3(WA_WARPS * 32), smem, st, d));
+  VY_CHECK_ARG(p->dim <= 32 * WA_VR, "vy_window_attn: dim %d > %d", p->dim, 32 * WA_VR);
+  if (p->max_new >= WA_TILED_MIN) {   // prompt-sized: 64 x 64 register-tiled form
+    VY_CUDA_OK(launch_window_attn_tiled(d, p->n_seqs, p->max_new, st));
+  } else if (p->max_new == 1) {
+    const size_t smem = sizeof(float) * (2 * WD_WARPS + static_cast<size_t>(WD_WARPS) * p->vdim);
+    VY_CUDA_OK(launch_kernel(window_attn_decode_kernel, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d));
   } else {
-    VY_CUDA_OK(launch_kernel(window_attn_kernel<false>, dim3((p->max_new + WA_WARPS - 1) / WA_WARPS, p->heads, p->n_seqs),
-                             dim3(WA_WARPS * 32), smem, st, d));
+    const size_t smem = sizeof(float) * static_cast<size_t>(WA_WARPS) * p->dim;
+    VY_CUDA_OK(launch_kernel(window_attn_kernel, dim3((p->max_new + WA_WARPS - 1) / WA_WARPS, p->heads, p->n_seqs), dim3(WA_WARPS * 32), smem,
+                             st, d));
   }
   VY_LAUNCH_OK();
   count_launch();
@@ -584,10 +738,11 @@ static cudaError_t launch_linear_attn(const RecDev& d, int n_seqs, cudaStream_t 
 }
 template <int DP>
 static cudaError_t launch_delta_rule(const RecDev& d, int n_seqs, cudaStream_t st) {
-  const int threads = col_threads(d.vdim);
+  const int threads = 128;   // 4 lanes per state column, 32 columns per CTA
   constexpr int CT = RecChunk<DP>::CT;
   const size_t smem = sizeof(float) * (3 * CT * DP + CT);
-  return launch_kernel(delta_rule_kernel<DP>, dim3((d.vdim + threads - 1) / threads, d.heads, n_seqs), dim3(threads), smem, st, d);
+  const int cols = threads / 4;
+  return launch_kernel(delta_rule_kernel<DP>, dim3((d.vdim + cols - 1) / cols, d.heads, n_seqs), dim3(threads), smem, st, d);
 }
 }  // namespace vy
 
@@ -610,7 +765,9 @@ extern "C" int vy_linear_attn(const VyLinAttn* p) {
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   cudaError_t e;
-  switch (pad_dim(p->dim)) {
+  if (p->max_new >= LA_CHUNKED_MIN && p->dim <= 128) {
+    e = launch_linear_attn_chunked(d, p->n_seqs, st);
+  } else switch (pad_dim(p->dim)) {
     case 16: e = launch_linear_attn<16>(d, p->n_seqs, st); break;
     case 32: e = launch_linear_attn<32>(d, p->n_seqs, st); break;
     case 64: e = launch_linear_attn<64>(d, p->n_seqs, st); break;

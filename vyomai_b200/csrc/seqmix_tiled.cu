@@ -1,0 +1,466 @@
+// Prompt-sized forms of two sequence mixers, in fp32 on register tiles (scores, softmax weights, decays and recurrent state
+// are 32-bit by the models' definition, so the contractions run on the FMA pipes, not on the 16-bit tensor-core path):
+//
+//   * linear attention with a fixed decay, chunk by chunk: for a chunk of C tokens with the state S0 before it,
+//       O = (Q K^T . D) V + diag(decay^(i+1)) Q S0,   D[i][j] = decay^(i-j) for j <= i, else 0
+//       S = decay^C S0 + sum_j decay^(C-1-j) k_j v_j^T
+//     one CTA owns (sequence, head, 64 value columns) and walks the chunks in order with its slice of S in shared memory;
+//   * windowed softmax attention with kept first tokens and a sink over pages: one CTA owns 64 queries of one head, walks
+//     the visible keys in tiles of 64 (the kept prefix first, then the window band) with an online softmax.
+//
+// Both give the same values as the token-serial kernels of seqmix.cu up to fp32 rounding, whatever the portion sizes.
+#include "seqmix.cuh"
+
+namespace vy {
+
+__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
+  acc = fmaf(a.x, b.x, acc);
+  acc = fmaf(a.y, b.y, acc);
+  acc = fmaf(a.z, b.z, acc);
+  return fmaf(a.w, b.w, acc);
+}
+__device__ __forceinline__ void axpy4(float (&acc)[4], const float a, const float4 x) {
+  acc[0] = fmaf(a, x.x, acc[0]);
+  acc[1] = fmaf(a, x.y, acc[1]);
+  acc[2] = fmaf(a, x.z, acc[2]);
+  acc[3] = fmaf(a, x.w, acc[3]);
+}
+__device__ __forceinline__ const float4& f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// Rows [0, rows) of a [rows, width] block of `src` into shared memory (row stride ld, zero-filled up to width4 columns, `act`
+// applied): row j starts at element off(j) of src, or is all zero when off(j) < 0. Global loads go out in batches of 8 per
+// thread before any of them is used, so a tile costs about one memory round trip. vec: src is fp32 and every row start and the
+// width are multiples of 4 elements (16-byte loads).
+template <int T, typename OffFn>
+__device__ __forceinline__ void rows_to_smem(float* dst, int ld, int rows, int width, int width4, const void* src, int dt, bool vec, int act,
+                                             OffFn off) {
+  constexpr int U = 8;
+  if (vec) {
+    const int w4 = width4 >> 2, total = rows * w4;
+    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < total) {
+          const int j = e / w4, c = (e - j * w4) << 2;
+          const long long o = off(j);
+          if (o >= 0 && c < width) v[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + o + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        if (e < total) {
+          const int j = e / w4, c = (e - j * w4) << 2;
+          if (act != VY_UACT_NONE) {
+            v[u].x = apply_uact(v[u].x, act); v[u].y = apply_uact(v[u].y, act);
+            v[u].z = apply_uact(v[u].z, act); v[u].w = apply_uact(v[u].w, act);
+          }
+          *reinterpret_cast<float4*>(dst + j * ld + c) = v[u];
+        }
+      }
+    }
+  } else {
+    const int total = rows * width4;
+    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        v[u] = 0.f;
+        if (e < total) {
+          const int j = e / width4, c = e - j * width4;
+          const long long o = off(j);
+          if (o >= 0 && c < width) v[u] = ld_as_float(src, dt, o + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        if (e < total) {
+          const int j = e / width4, c = e - j * width4;
+          dst[j * ld + c] = act != VY_UACT_NONE ? apply_uact(v[u], act) : v[u];
+        }
+      }
+    }
+  }
+}
+
+// ---- chunked linear attention ------------------------------------------------------------------------------------------
+constexpr int LA_C = 64;    // tokens per chunk
+constexpr int LA_VS = 64;   // value columns per CTA
+constexpr int LA_T = 256;   // threads: a 16 x 16 grid of 4 x 4 output tiles
+
+template <int DP>
+struct LaSmem {
+  static constexpr int LDQ = DP + 4;        // row stride of the q / k chunks (floats): rows 16 apart fall in distinct banks
+  static constexpr int LDV = LA_VS + 4;     // row stride of the v chunk, the weights P and the state slice
+  static constexpr int floats = 2 * LA_C * LDQ + 2 * LA_C * LDV + DP * LDV + LA_C + 4;
+};
+
+template <int DP>
+__global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bool vec) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int LDQ = LaSmem<DP>::LDQ, LDV = LaSmem<DP>::LDV;
+  constexpr int DR = DP / 16;               // state rows per thread in the update
+  extern __shared__ __align__(16) float la_smem[];
+  float* Qs = la_smem;                      // [C][LDQ]
+  float* Ks = Qs + LA_C * LDQ;              // [C][LDQ]
+  float* Vs = Ks + LA_C * LDQ;              // [C][LDV]
+  float* Ps = Vs + LA_C * LDV;              // [C][LDV]
+  float* Ss = Ps + LA_C * LDV;              // [DP][LDV]
+  float* pw = Ss + DP * LDV;                // decay^n, n = 0 .. C
+  const int s = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * LA_VS;
+  const int t = threadIdx.x, ti = t >> 4, tj = t & 15;
+  const int base = d.cu[s], n = d.cu[s + 1] - base;
+  if (n <= 0) return;
+  if (t <= LA_C) pw[t] = static_cast<float>(pow(static_cast<double>(d.decay[h]), static_cast<double>(t)));
+  float* sp = d.state + (static_cast<long long>(d.slot[s]) * d.heads + h) * d.dim * d.vdim;
+  const bool carried = d.pos0[s] > 0;
+  for (int e = t; e < DP * LA_VS; e += LA_T) {
+    const int i = e / LA_VS, c = e % LA_VS;
+    Ss[i * LDV + c] = (carried && i < d.dim && v0 + c < d.vdim) ? sp[static_cast<long long>(i) * d.vdim + v0 + c] : 0.f;
+  }
+  for (int t0 = 0; t0 < n; t0 += LA_C) {
+    const int nt = min(LA_C, n - t0);
+    __syncthreads();
+    {
+      const long long r0 = base + t0;
+      rows_to_smem<LA_T>(Qs, LDQ, LA_C, d.dim, DP, d.q, d.in_dt, vec, d.in_act,
+                         [&](int tt) { return tt < nt ? (r0 + tt) * d.ldq + static_cast<long long>(h) * d.dim : -1LL; });
+      rows_to_smem<LA_T>(Ks, LDQ, LA_C, d.dim, DP, d.k, d.in_dt, vec, d.in_act,
+                         [&](int tt) { return tt < nt ? (r0 + tt) * d.ldk + static_cast<long long>(h) * d.dim : -1LL; });
+      rows_to_smem<LA_T>(Vs, LDV, LA_C, min(LA_VS, d.vdim - v0), LA_VS, d.v, d.in_dt, vec, d.in_act,
+                         [&](int tt) { return tt < nt ? (r0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + v0 : -1LL; });
+    }
+    __syncthreads();
+    // what the earlier chunks left: oi[r][e] = sum_i Q[ti + 16 r][i] S0[i][4 tj + e]
+    float oi[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oi[r][e] = 0.f;
+#pragma unroll 2
+    for (int d4 = 0; d4 < DP; d4 += 4) {
+      const float4 s0 = f4(Ss + (d4 + 0) * LDV + 4 * tj), s1 = f4(Ss + (d4 + 1) * LDV + 4 * tj);
+      const float4 s2 = f4(Ss + (d4 + 2) * LDV + 4 * tj), s3 = f4(Ss + (d4 + 3) * LDV + 4 * tj);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 qv = f4(Qs + (ti + 16 * r) * LDQ + d4);
+        axpy4(oi[r], qv.x, s0);
+        axpy4(oi[r], qv.y, s1);
+        axpy4(oi[r], qv.z, s2);
+        axpy4(oi[r], qv.w, s3);
+      }
+    }
+    // weights inside the chunk: P[i][j] = (q_i . k_j) decay^(i-j) for j <= i; rows ti + 16 r, columns tj + 16 c, blocks c <= r
+    float p[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) p[r][c] = 0.f;
+#pragma unroll 2
+    for (int d4 = 0; d4 < DP; d4 += 4) {
+      float4 kv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kv[c] = f4(Ks + (tj + 16 * c) * LDQ + d4);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 qv = f4(Qs + (ti + 16 * r) * LDQ + d4);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (c <= r) p[r][c] = dot4(qv, kv[c], p[r][c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = ti + 16 * r, j = tj + 16 * c;
+        Ps[i * LDV + j] = (c <= r && j <= i && i < nt) ? p[r][c] * pw[i - j] : 0.f;
+      }
+    __syncthreads();
+    // inside the chunk: oa[r][e] = sum_j P[ti + 16 r][j] V[j][4 tj + e]; row block r only sees j < 16 (r + 1)
+    float oa[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oa[r][e] = 0.f;
+#pragma unroll
+    for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll
+      for (int j4 = 16 * jb; j4 < 16 * jb + 16; j4 += 4) {
+        const float4 x0 = f4(Vs + (j4 + 0) * LDV + 4 * tj), x1 = f4(Vs + (j4 + 1) * LDV + 4 * tj);
+        const float4 x2 = f4(Vs + (j4 + 2) * LDV + 4 * tj), x3 = f4(Vs + (j4 + 3) * LDV + 4 * tj);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          if (r >= jb) {
+            const float4 pv = f4(Ps + (ti + 16 * r) * LDV + j4);
+            axpy4(oa[r], pv.x, x0);
+            axpy4(oa[r], pv.y, x1);
+            axpy4(oa[r], pv.z, x2);
+            axpy4(oa[r], pv.w, x3);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = ti + 16 * r;
+      if (i < nt) {
+        const float wi = pw[i + 1];
+        const long long o = static_cast<long long>(base + t0 + i) * d.ld_out + static_cast<long long>(h) * d.vdim + v0 + 4 * tj;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (v0 + 4 * tj + e < d.vdim) st_from_float(d.out, d.out_dt, o + e, fmaf(wi, oi[r][e], oa[r][e]));
+      }
+    }
+    // the state after the chunk: rows ti DR .. ti DR + DR - 1, columns 4 tj .. 4 tj + 3 (each thread owns its tile of Ss)
+    float sa[DR][4];
+#pragma unroll
+    for (int x = 0; x < DR; ++x)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sa[x][e] = 0.f;
+    for (int j = 0; j < nt; ++j) {
+      const float w = pw[nt - 1 - j];
+      float4 vv = f4(Vs + j * LDV + 4 * tj);
+      vv.x *= w; vv.y *= w; vv.z *= w; vv.w *= w;
+      float kk[DR];
+      if constexpr (DR % 4 == 0) {
+#pragma unroll
+        for (int x = 0; x < DR; x += 4) {
+          const float4 k4 = f4(Ks + j * LDQ + ti * DR + x);
+          kk[x] = k4.x; kk[x + 1] = k4.y; kk[x + 2] = k4.z; kk[x + 3] = k4.w;
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < DR; ++x) kk[x] = Ks[j * LDQ + ti * DR + x];
+      }
+#pragma unroll
+      for (int x = 0; x < DR; ++x) axpy4(sa[x], kk[x], vv);
+    }
+    const float wc = pw[nt];
+#pragma unroll
+    for (int x = 0; x < DR; ++x) {
+      float* sr = Ss + (ti * DR + x) * LDV + 4 * tj;
+      float4 o = f4(sr);
+      o.x = fmaf(wc, o.x, sa[x][0]);
+      o.y = fmaf(wc, o.y, sa[x][1]);
+      o.z = fmaf(wc, o.z, sa[x][2]);
+      o.w = fmaf(wc, o.w, sa[x][3]);
+      *reinterpret_cast<float4*>(sr) = o;
+    }
+  }
+  __syncthreads();
+  for (int e = t; e < DP * LA_VS; e += LA_T) {
+    const int i = e / LA_VS, c = e % LA_VS;
+    if (i < d.dim && v0 + c < d.vdim) sp[static_cast<long long>(i) * d.vdim + v0 + c] = Ss[i * LDV + c];
+  }
+}
+
+template <int DP>
+static cudaError_t launch_la(const RecDev& d, int n_seqs, cudaStream_t st) {
+  constexpr size_t smem = sizeof(float) * LaSmem<DP>::floats;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = cudaFuncSetAttribute(linear_attn_chunk_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    once = true;
+  }
+  const auto al = [](const void* p, long long ld) { return reinterpret_cast<uintptr_t>(p) % 16 == 0 && ld % 4 == 0; };
+  const bool vec = d.in_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.q, d.ldq) && al(d.k, d.ldk) && al(d.v, d.ldv);
+  return launch_kernel(linear_attn_chunk_kernel<DP>, dim3((d.vdim + LA_VS - 1) / LA_VS, d.heads, n_seqs), dim3(LA_T), smem, st, d, vec);
+}
+
+cudaError_t launch_linear_attn_chunked(const RecDev& d, int n_seqs, cudaStream_t st) {
+  if (d.dim <= 16) return launch_la<16>(d, n_seqs, st);
+  if (d.dim <= 32) return launch_la<32>(d, n_seqs, st);
+  if (d.dim <= 64) return launch_la<64>(d, n_seqs, st);
+  return launch_la<128>(d, n_seqs, st);   // callers keep dim <= 128 here
+}
+
+
+// ---- tiled windowed attention --------------------------------------------------------------------------------------------
+constexpr int WT_M = 64;            // queries per CTA
+constexpr int WT_N = 64;            // keys per tile
+constexpr int WT_T = 256;           // threads: 16 x 16, each 4 query rows (ti + 16 r) by 4 key columns (tj + 16 c)
+constexpr int WT_LDP = WT_N + 4;
+
+template <int MV>
+__global__ void __launch_bounds__(WT_T, 1) window_attn_tiled_kernel(WinDev d, int ldq_s, int ldv_s, int dim4, int vdim4, bool qvec, bool kvvec) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float wt_smem[];
+  float* Qs = wt_smem;                       // [WT_M][ldq_s]
+  float* Ks = Qs + WT_M * ldq_s;             // [WT_N][ldq_s]
+  float* Vs = Ks + WT_N * ldq_s;             // [WT_N][ldv_s]
+  float* Ps = Vs + WT_N * ldv_s;             // [WT_M][WT_LDP]
+  float* corr_s = Ps + WT_M * WT_LDP;        // [WT_M]
+  float* l_s = corr_s + WT_M;                // [WT_M]
+  int* kpos_s = reinterpret_cast<int*>(l_s + WT_M);   // [WT_N] key position, -1 past the end
+  int* krow_s = kpos_s + WT_N;                        // [WT_N] its row in the pools
+  const int s = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * WT_M;
+  const int t = threadIdx.x, ti = t >> 4, tj = t & 15, warp = t >> 5, lane = t & 31;
+  const int base = d.cu[s], n = d.cu[s + 1] - base;
+  if (i0 >= n) return;
+  const int rows = min(WT_M, n - i0);
+  const int g = h / (d.heads / d.kv_heads);
+  rows_to_smem<WT_T>(Qs, ldq_s, WT_M, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE,
+               [&](int i) { return i < rows ? static_cast<long long>(base + i0 + i) * d.ldq + static_cast<long long>(h) * d.dim : -1LL; });
+  const int p_lo = d.pos0[s] + i0, p_hi = p_lo + rows - 1;
+  // visible keys of the tile's queries: [0, nA) (kept first tokens outside the band) and [lo, p_hi] (the band); masks are per pair
+  const int lo = d.window <= 0 ? 0 : max(p_lo - d.window + 1, 0);
+  const int nA = d.window <= 0 ? 0 : min(d.keep, lo);
+  const int count = nA + (p_hi - lo + 1);
+  const int* tab = d.table + static_cast<long long>(s) * d.tw;
+  float m[8], l[8];   // softmax statistics of rows 8 warp .. 8 warp + 7, the same in every lane
+#pragma unroll
+  for (int rr = 0; rr < 8; ++rr) {
+    m[rr] = d.sink ? ld_as_float(d.sink, d.sink_dt, h) : -INFINITY;
+    l[rr] = d.sink ? 1.f : 0.f;
+  }
+  float acc[4][MV][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[r][mm][e] = 0.f;
+  const long long kstride = static_cast<long long>(d.kv_heads) * d.dim, vstride = static_cast<long long>(d.kv_heads) * d.vdim;
+  for (int c0 = 0; c0 < count; c0 += WT_N) {
+    __syncthreads();
+    if (t < WT_N) {
+      const int c = c0 + t;
+      const int kp = c < count ? (c < nA ? c : lo + (c - nA)) : -1;
+      kpos_s[t] = kp;
+      krow_s[t] = kp >= 0 ? tab[kp / d.bs] * d.bs + kp % d.bs : 0;
+    }
+    __syncthreads();
+    rows_to_smem<WT_T>(Ks, ldq_s, WT_N, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE,
+                 [&](int j) { return kpos_s[j] >= 0 ? static_cast<long long>(krow_s[j]) * kstride + static_cast<long long>(g) * d.dim : -1LL; });
+    rows_to_smem<WT_T>(Vs, ldv_s, WT_N, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE,
+                 [&](int j) { return kpos_s[j] >= 0 ? static_cast<long long>(krow_s[j]) * vstride + static_cast<long long>(g) * d.vdim : -1LL; });
+    __syncthreads();
+    float sc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sc[r][c] = 0.f;
+#pragma unroll 2
+    for (int d4 = 0; d4 < dim4; d4 += 4) {
+      float4 kv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kv[c] = f4(Ks + (tj + 16 * c) * ldq_s + d4);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 qv = f4(Qs + (ti + 16 * r) * ldq_s + d4);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[r][c] = dot4(qv, kv[c], sc[r][c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = ti + 16 * r, j = tj + 16 * c;
+        const int p = p_lo + i, kp = kpos_s[j];
+        const bool vis = i < rows && kp >= 0 && kp <= p && (d.window <= 0 || p - kp < d.window || kp < d.keep);
+        Ps[i * WT_LDP + j] = vis ? sc[r][c] * d.scale : -INFINITY;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < 8; ++rr) {
+      float* pr = Ps + (8 * warp + rr) * WT_LDP;
+      const float a = pr[lane], b = pr[lane + 32];
+      const float mn = fmaxf(m[rr], warp_max(fmaxf(a, b)));
+      const float cr = mn == -INFINITY ? 1.f : expf(m[rr] - mn);
+      const float pa = a == -INFINITY ? 0.f : expf(a - mn), pb = b == -INFINITY ? 0.f : expf(b - mn);
+      pr[lane] = pa;
+      pr[lane + 32] = pb;
+      l[rr] = fmaf(l[rr], cr, warp_sum(pa + pb));
+      m[rr] = mn;
+      if (lane == 0) corr_s[8 * warp + rr] = cr;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float cr = corr_s[ti + 16 * r];
+#pragma unroll
+      for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[r][mm][e] *= cr;
+    }
+    const int nv = min(WT_N, (count - c0 + 3) & ~3);
+    for (int j4 = 0; j4 < nv; j4 += 4) {
+      float4 pv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) pv[r] = f4(Ps + (ti + 16 * r) * WT_LDP + j4);
+#pragma unroll
+      for (int mm = 0; mm < MV; ++mm) {
+        const int col = 4 * (tj + 16 * mm);
+        if (col < vdim4) {
+          const float4 x0 = f4(Vs + (j4 + 0) * ldv_s + col), x1 = f4(Vs + (j4 + 1) * ldv_s + col);
+          const float4 x2 = f4(Vs + (j4 + 2) * ldv_s + col), x3 = f4(Vs + (j4 + 3) * ldv_s + col);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            axpy4(acc[r][mm], pv[r].x, x0);
+            axpy4(acc[r][mm], pv[r].y, x1);
+            axpy4(acc[r][mm], pv[r].z, x2);
+            axpy4(acc[r][mm], pv[r].w, x3);
+          }
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int rr = 0; rr < 8; ++rr) l_s[8 * warp + rr] = l[rr];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = ti + 16 * r;
+    if (i >= rows) continue;
+    const long long qrow = base + i0 + i;
+    float og = 1.f / l_s[i];
+    if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
+#pragma unroll
+    for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = 4 * (tj + 16 * mm) + e;
+        if (col < d.vdim) st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, acc[r][mm][e] * og);
+      }
+  }
+}
+
+template <int MV>
+static cudaError_t launch_wt(const WinDev& d, int n_seqs, int max_new, cudaStream_t st) {
+  const int dim4 = (d.dim + 3) & ~3, vdim4 = (d.vdim + 3) & ~3;
+  const int ldq_s = ((dim4 >> 2) & 1) ? dim4 + 8 : dim4 + 4;   // (row stride / 4) odd: rows 1 apart start in distinct 16-byte bank groups
+  const int ldv_s = vdim4 + 4;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(WT_M + WT_N) * ldq_s + static_cast<size_t>(WT_N) * ldv_s + WT_M * WT_LDP + 2 * WT_M) +
+                      sizeof(int) * 2 * WT_N;
+  const auto al = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool qvec = d.q_dt == VY_F32 && d.dim % 4 == 0 && d.ldq % 4 == 0 && al(d.q);
+  const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.kp) && al(d.vp);
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(window_attn_tiled_kernel<MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    allowed = smem;
+  }
+  return launch_kernel(window_attn_tiled_kernel<MV>, dim3((max_new + WT_M - 1) / WT_M, d.heads, n_seqs), dim3(WT_T), smem, st, d, ldq_s, ldv_s,
+                       dim4, vdim4, qvec, kvvec);
+}
+
+cudaError_t launch_window_attn_tiled(const WinDev& d, int n_seqs, int max_new, cudaStream_t st) {
+  if (d.vdim <= 64) return launch_wt<1>(d, n_seqs, max_new, st);
+  if (d.vdim <= 128) return launch_wt<2>(d, n_seqs, max_new, st);
+  return launch_wt<4>(d, n_seqs, max_new, st);   // vdim <= 256 (checked by the caller)
+}
+
+}  // namespace vy
