@@ -55,6 +55,7 @@ enum {
   VY_ACT_DGELU_ERF = 3,
   VY_ACT_DGELU_TANH = 4,
   VY_ACT_SWIGLU = 5, /* gated MLP: see VyGemm.act */
+  VY_ACT_RELU2 = 7, /* max(x, 0)^2 */
   VY_ACT_GEGLU_TANH = 6 /* same layout and rules as VY_ACT_SWIGLU with out = gelu_tanh(gate) * up (GemmaMLP, Examples/paligemma.ipynb cell 11) */
 };
 

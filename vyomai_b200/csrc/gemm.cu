@@ -296,7 +296,7 @@ extern "C" int vy_gemm(const VyGemm* p) {
 
   if (p->epi == VY_EPI_LINEAR) {
     VY_CHECK_ARG(p->out != nullptr && dtype_ok(p->out_dtype), "vy_gemm: out / out_dtype invalid");
-    VY_CHECK_ARG(p->act >= VY_ACT_NONE && p->act <= VY_ACT_SWIGLU, "vy_gemm: bad act %d", p->act);
+    VY_CHECK_ARG((p->act >= VY_ACT_NONE && p->act <= VY_ACT_SWIGLU) || p->act == VY_ACT_RELU2, "vy_gemm: bad act %d", p->act);
     if (p->act == VY_ACT_SWIGLU)
       VY_CHECK_ARG((p->N & 1) == 0 && !p->addend && !p->addend2 && !p->transposed_out && p->out_row_group == 0,
                    "vy_gemm: SWIGLU needs an even N (interleaved gate/up rows) and takes no addend / transpose / row remap");

@@ -104,6 +104,7 @@ struct GemmCfg {
 __device__ __forceinline__ float apply_act(int act, float x) {
   if (act == VY_ACT_GELU_ERF) return gelu_erf(x);
   if (act == VY_ACT_GELU_TANH) return gelu_tanh(x);
+  if (act == VY_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
   return x;
 }
 __device__ __forceinline__ float apply_dact(int act, float z) {
@@ -173,7 +174,7 @@ __device__ __forceinline__ float gate_fn(float x, int gate_act) { return gate_ac
 static __device__ __noinline__ void epilogue_chunk_general(const GemmDev& g, const uint32_t* raw, const float* bs, int grow,
                                                     long long orow, long long arow, int gcol0, int lim) {
   const float scale = g.out_scale == 0.f ? 1.f : g.out_scale;
-  const bool fwd_act = g.act == VY_ACT_GELU_ERF || g.act == VY_ACT_GELU_TANH;
+  const bool fwd_act = g.act == VY_ACT_GELU_ERF || g.act == VY_ACT_GELU_TANH || g.act == VY_ACT_RELU2;
   const bool bwd_act = g.act == VY_ACT_DGELU_ERF || g.act == VY_ACT_DGELU_TANH;
   if (g.act == VY_ACT_SWIGLU) {
     // columns (2j, 2j+1) of the accumulator are (gate_j, up_j): 32 accumulator columns -> 16 outputs at column gcol0 / 2
@@ -637,7 +638,7 @@ __device__ __forceinline__ void epilogue_transposed(const GemmDev& g, uint32_t t
   constexpr int NCH = BN >= 32 ? BN / 32 : 1;
   constexpr int LDT = 128 + 1;
   const float scale = g.out_scale == 0.f ? 1.f : g.out_scale;
-  const bool fwd_act = g.act == VY_ACT_GELU_ERF || g.act == VY_ACT_GELU_TANH;
+  const bool fwd_act = g.act == VY_ACT_GELU_ERF || g.act == VY_ACT_GELU_TANH || g.act == VY_ACT_RELU2;
   const bool bwd_act = g.act == VY_ACT_DGELU_ERF || g.act == VY_ACT_DGELU_TANH;
   mbar_wait_soft(tfull_bar, tfull_phase, g.poison);
   tc_fence_after();

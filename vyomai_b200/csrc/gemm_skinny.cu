@@ -172,6 +172,7 @@ gemm_skinny_kernel(const SkinnyDev p) {
       if (p.bias) x += ld_as_float(p.bias, p.bias_dt, f + j);
       if (p.act == VY_ACT_GELU_ERF) x = gelu_erf(x);
       else if (p.act == VY_ACT_GELU_TANH) x = gelu_tanh(x);
+      else if (p.act == VY_ACT_RELU2) { x = fmaxf(x, 0.f); x *= x; }
       if (p.addend) x += ld_as_float(p.addend, p.addend_dt, static_cast<long long>(tok) * p.ld_addend + f + j);
       v[j] = x * scale;
     }
@@ -231,7 +232,7 @@ bool skinny_applicable(const VyGemm* p) {
   if (off) return false;
   if (p->epi != VY_EPI_LINEAR || p->in_dtype != VY_BF16 || !p->transposed_out || p->a_mn_major || p->b_mn_major) return false;
   if (p->N > 32 || p->aux || p->addend2 || p->addend_row_mod || p->out_row_group) return false;
-  if (p->act != VY_ACT_NONE && p->act != VY_ACT_GELU_ERF && p->act != VY_ACT_GELU_TANH) return false;
+  if (p->act != VY_ACT_NONE && p->act != VY_ACT_GELU_ERF && p->act != VY_ACT_GELU_TANH && p->act != VY_ACT_RELU2) return false;
   // one wave of small CTAs is the whole point; a vocabulary-sized F (3142 feature blocks) would run ~4 latency-bound waves of
   // them and measured 2x slower than the 128-row tensor-memory tiles, which stream 77 MB at 3.5 TB/s
   if ((p->M + 15) / 16 > 4 * num_sms()) return false;

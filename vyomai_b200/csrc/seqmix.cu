@@ -485,6 +485,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
   float (*ks)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem + CT * DP);
   float (*gs)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem + 2 * CT * DP);
   float* betas = dr_smem + 3 * CT * DP;
+  float* vs = betas + CT;                       // [CT][32]: the chunk's values of this CTA's 32 columns
   const int s = blockIdx.z, h = blockIdx.y;
   const int part = threadIdx.x & 3;
   const int j = blockIdx.x * 32 + (threadIdx.x >> 2);
@@ -507,7 +508,8 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     }
   // the next chunk's raw q / k / decay inputs travel in registers while the current chunk is walked
   constexpr int NPF = CT * DP / 128;
-  float rq[NPF], rk[NPF], ra[NPF], rb = 0.f;
+  constexpr int NV = CT * 32 / 128;
+  float rq[NPF], rk[NPF], ra[NPF], rv[NV], rb = 0.f;
   auto fetch = [&](int t0) {
     const int nt = min(CT, n - t0);
 #pragma unroll
@@ -518,6 +520,11 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
       rq[u] = ok ? ld_as_float(d.q, d.in_dt, row * d.ldq + static_cast<long long>(gq) * d.dim + i) : 0.f;
       rk[u] = ok ? ld_as_float(d.k, d.in_dt, row * d.ldk + static_cast<long long>(gq) * d.dim + i) : 0.f;
       ra[u] = ok ? ld_as_float(d.a, d.a_dt, row * d.ld_a + static_cast<long long>(h) * d.dim + i) : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const int e = threadIdx.x + u * 128, tt = e >> 5, c = static_cast<int>(blockIdx.x) * 32 + (e & 31);
+      rv[u] = (tt < nt && c < d.vdim) ? ld_as_float(d.v, d.in_dt, static_cast<long long>(base + t0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + c) : 0.f;
     }
     if (threadIdx.x < nt) rb = ld_as_float(d.b, d.b_dt, static_cast<long long>(base + t0 + threadIdx.x) * d.ld_b + h);
   };
@@ -532,6 +539,8 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
       ks[tt][i] = rk[u];
       gs[tt][i] = ra[u] == -INFINITY ? 1.f : expf(neg_rate * softplusf_(ra[u]));
     }
+#pragma unroll
+    for (int u = 0; u < NV; ++u) vs[threadIdx.x + u * 128] = rv[u];
     if (threadIdx.x < nt) betas[threadIdx.x] = sigmoidf_(rb);
     __syncthreads();
     for (int tt = warp; tt < nt; tt += nwarps) {
@@ -552,7 +561,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     if (t0 + CT < n) fetch(t0 + CT);
     for (int tt = 0; tt < nt; ++tt) {
       const long long row = base + t0 + tt;
-      const float vj = active ? ld_as_float(d.v, d.in_dt, row * d.ldv + static_cast<long long>(h) * d.vdim + j) : 0.f;
+      const float vj = vs[tt * 32 + (threadIdx.x >> 2)];
       float4 k4[NM];
       float r0 = 0.f, r1 = 0.f;
 #pragma unroll
@@ -740,7 +749,7 @@ template <int DP>
 static cudaError_t launch_delta_rule(const RecDev& d, int n_seqs, cudaStream_t st) {
   const int threads = 128;   // 4 lanes per state column, 32 columns per CTA
   constexpr int CT = RecChunk<DP>::CT;
-  const size_t smem = sizeof(float) * (3 * CT * DP + CT);
+  const size_t smem = sizeof(float) * (3 * CT * DP + CT + CT * 32);
   const int cols = threads / 4;
   return launch_kernel(delta_rule_kernel<DP>, dim3((d.vdim + cols - 1) / cols, d.heads, n_seqs), dim3(threads), smem, st, d);
 }

@@ -90,38 +90,55 @@ __device__ __forceinline__ void rows_to_smem(float* dst, int ld, int rows, int w
 
 // ---- chunked linear attention ------------------------------------------------------------------------------------------
 constexpr int LA_C = 64;    // tokens per chunk
-constexpr int LA_VS = 64;   // value columns per CTA
-constexpr int LA_T = 256;   // threads: a 16 x 16 grid of 4 x 4 output tiles
+constexpr int LA_T = 256;   // threads: a 16 x 16 grid; thread (ti, tj) owns rows ti + 16 r and VS / 16 adjacent value columns
+constexpr int LA_LDP = LA_C + 4;
 
-template <int DP>
+template <int DP, int VS>   // VS: value columns per CTA, 32 (two CTAs per SM, more CTAs) or 64 (less repeated work)
 struct LaSmem {
-  static constexpr int LDQ = DP + 4;        // row stride of the q / k chunks (floats): rows 16 apart fall in distinct banks
-  static constexpr int LDV = LA_VS + 4;     // row stride of the v chunk, the weights P and the state slice
-  static constexpr int floats = 2 * LA_C * LDQ + 2 * LA_C * LDV + DP * LDV + LA_C + 4;
+  static constexpr int LDQ = DP + 4;    // row stride of the q / k chunks (floats): rows 1 apart start in distinct 16-byte bank groups
+  static constexpr int LDV = VS + 4;    // row stride of the v chunk and the state slice
+  static constexpr int floats = 2 * LA_C * LDQ + LA_C * LDV + LA_C * LA_LDP + DP * LDV + LA_C + 4;
 };
 
-template <int DP>
-__global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bool vec) {
+template <int NV>
+__device__ __forceinline__ void ldv(const float* p, float (&x)[NV]) {
+  if constexpr (NV == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    x[0] = v.x; x[1] = v.y;
+  }
+}
+template <int NV>
+__device__ __forceinline__ void axpyv(float (&acc)[NV], const float a, const float (&x)[NV]) {
+#pragma unroll
+  for (int e = 0; e < NV; ++e) acc[e] = fmaf(a, x[e], acc[e]);
+}
+
+template <int DP, int VS>
+__global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kernel(RecDev d, bool vec) {
   pdl_trigger();
   pdl_wait();
-  constexpr int LDQ = LaSmem<DP>::LDQ, LDV = LaSmem<DP>::LDV;
+  constexpr int LDQ = LaSmem<DP, VS>::LDQ, LDV = LaSmem<DP, VS>::LDV, LDP = LA_LDP;
+  constexpr int NV = VS / 16;               // value columns per thread
   constexpr int DR = DP / 16;               // state rows per thread in the update
   extern __shared__ __align__(16) float la_smem[];
   float* Qs = la_smem;                      // [C][LDQ]
   float* Ks = Qs + LA_C * LDQ;              // [C][LDQ]
   float* Vs = Ks + LA_C * LDQ;              // [C][LDV]
-  float* Ps = Vs + LA_C * LDV;              // [C][LDV]
-  float* Ss = Ps + LA_C * LDV;              // [DP][LDV]
+  float* Ps = Vs + LA_C * LDV;              // [C][LDP]
+  float* Ss = Ps + LA_C * LDP;              // [DP][LDV]
   float* pw = Ss + DP * LDV;                // decay^n, n = 0 .. C
-  const int s = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * LA_VS;
+  const int s = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * VS;
   const int t = threadIdx.x, ti = t >> 4, tj = t & 15;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
   if (n <= 0) return;
   if (t <= LA_C) pw[t] = static_cast<float>(pow(static_cast<double>(d.decay[h]), static_cast<double>(t)));
   float* sp = d.state + (static_cast<long long>(d.slot[s]) * d.heads + h) * d.dim * d.vdim;
   const bool carried = d.pos0[s] > 0;
-  for (int e = t; e < DP * LA_VS; e += LA_T) {
-    const int i = e / LA_VS, c = e % LA_VS;
+  for (int e = t; e < DP * VS; e += LA_T) {
+    const int i = e / VS, c = e % VS;
     Ss[i * LDV + c] = (carried && i < d.dim && v0 + c < d.vdim) ? sp[static_cast<long long>(i) * d.vdim + v0 + c] : 0.f;
   }
   for (int t0 = 0; t0 < n; t0 += LA_C) {
@@ -133,27 +150,30 @@ __global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bo
                          [&](int tt) { return tt < nt ? (r0 + tt) * d.ldq + static_cast<long long>(h) * d.dim : -1LL; });
       rows_to_smem<LA_T>(Ks, LDQ, LA_C, d.dim, DP, d.k, d.in_dt, vec, d.in_act,
                          [&](int tt) { return tt < nt ? (r0 + tt) * d.ldk + static_cast<long long>(h) * d.dim : -1LL; });
-      rows_to_smem<LA_T>(Vs, LDV, LA_C, min(LA_VS, d.vdim - v0), LA_VS, d.v, d.in_dt, vec, d.in_act,
+      rows_to_smem<LA_T>(Vs, LDV, LA_C, min(VS, d.vdim - v0), VS, d.v, d.in_dt, vec, d.in_act,
                          [&](int tt) { return tt < nt ? (r0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + v0 : -1LL; });
     }
     __syncthreads();
-    // what the earlier chunks left: oi[r][e] = sum_i Q[ti + 16 r][i] S0[i][4 tj + e]
-    float oi[4][4];
+    // what the earlier chunks left: oi[r][e] = sum_i Q[ti + 16 r][i] S0[i][NV tj + e]
+    float oi[4][NV];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) oi[r][e] = 0.f;
+      for (int e = 0; e < NV; ++e) oi[r][e] = 0.f;
 #pragma unroll 2
     for (int d4 = 0; d4 < DP; d4 += 4) {
-      const float4 s0 = f4(Ss + (d4 + 0) * LDV + 4 * tj), s1 = f4(Ss + (d4 + 1) * LDV + 4 * tj);
-      const float4 s2 = f4(Ss + (d4 + 2) * LDV + 4 * tj), s3 = f4(Ss + (d4 + 3) * LDV + 4 * tj);
+      float s0[NV], s1[NV], s2[NV], s3[NV];
+      ldv<NV>(Ss + (d4 + 0) * LDV + NV * tj, s0);
+      ldv<NV>(Ss + (d4 + 1) * LDV + NV * tj, s1);
+      ldv<NV>(Ss + (d4 + 2) * LDV + NV * tj, s2);
+      ldv<NV>(Ss + (d4 + 3) * LDV + NV * tj, s3);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float4 qv = f4(Qs + (ti + 16 * r) * LDQ + d4);
-        axpy4(oi[r], qv.x, s0);
-        axpy4(oi[r], qv.y, s1);
-        axpy4(oi[r], qv.z, s2);
-        axpy4(oi[r], qv.w, s3);
+        axpyv<NV>(oi[r], qv.x, s0);
+        axpyv<NV>(oi[r], qv.y, s1);
+        axpyv<NV>(oi[r], qv.z, s2);
+        axpyv<NV>(oi[r], qv.w, s3);
       }
     }
     // weights inside the chunk: P[i][j] = (q_i . k_j) decay^(i-j) for j <= i; rows ti + 16 r, columns tj + 16 c, blocks c <= r
@@ -180,29 +200,32 @@ __global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bo
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int i = ti + 16 * r, j = tj + 16 * c;
-        Ps[i * LDV + j] = (c <= r && j <= i && i < nt) ? p[r][c] * pw[i - j] : 0.f;
+        Ps[i * LDP + j] = (c <= r && j <= i && i < nt) ? p[r][c] * pw[i - j] : 0.f;
       }
     __syncthreads();
-    // inside the chunk: oa[r][e] = sum_j P[ti + 16 r][j] V[j][4 tj + e]; row block r only sees j < 16 (r + 1)
-    float oa[4][4];
+    // inside the chunk: oa[r][e] = sum_j P[ti + 16 r][j] V[j][NV tj + e]; row block r only sees j < 16 (r + 1)
+    float oa[4][NV];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) oa[r][e] = 0.f;
+      for (int e = 0; e < NV; ++e) oa[r][e] = 0.f;
 #pragma unroll
     for (int jb = 0; jb < 4; ++jb) {
 #pragma unroll
       for (int j4 = 16 * jb; j4 < 16 * jb + 16; j4 += 4) {
-        const float4 x0 = f4(Vs + (j4 + 0) * LDV + 4 * tj), x1 = f4(Vs + (j4 + 1) * LDV + 4 * tj);
-        const float4 x2 = f4(Vs + (j4 + 2) * LDV + 4 * tj), x3 = f4(Vs + (j4 + 3) * LDV + 4 * tj);
+        float x0[NV], x1[NV], x2[NV], x3[NV];
+        ldv<NV>(Vs + (j4 + 0) * LDV + NV * tj, x0);
+        ldv<NV>(Vs + (j4 + 1) * LDV + NV * tj, x1);
+        ldv<NV>(Vs + (j4 + 2) * LDV + NV * tj, x2);
+        ldv<NV>(Vs + (j4 + 3) * LDV + NV * tj, x3);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           if (r >= jb) {
-            const float4 pv = f4(Ps + (ti + 16 * r) * LDV + j4);
-            axpy4(oa[r], pv.x, x0);
-            axpy4(oa[r], pv.y, x1);
-            axpy4(oa[r], pv.z, x2);
-            axpy4(oa[r], pv.w, x3);
+            const float4 pv = f4(Ps + (ti + 16 * r) * LDP + j4);
+            axpyv<NV>(oa[r], pv.x, x0);
+            axpyv<NV>(oa[r], pv.y, x1);
+            axpyv<NV>(oa[r], pv.z, x2);
+            axpyv<NV>(oa[r], pv.w, x3);
           }
         }
       }
@@ -212,22 +235,25 @@ __global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bo
       const int i = ti + 16 * r;
       if (i < nt) {
         const float wi = pw[i + 1];
-        const long long o = static_cast<long long>(base + t0 + i) * d.ld_out + static_cast<long long>(h) * d.vdim + v0 + 4 * tj;
+        const long long o = static_cast<long long>(base + t0 + i) * d.ld_out + static_cast<long long>(h) * d.vdim + v0 + NV * tj;
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (v0 + 4 * tj + e < d.vdim) st_from_float(d.out, d.out_dt, o + e, fmaf(wi, oi[r][e], oa[r][e]));
+        for (int e = 0; e < NV; ++e)
+          if (v0 + NV * tj + e < d.vdim) st_from_float(d.out, d.out_dt, o + e, fmaf(wi, oi[r][e], oa[r][e]));
       }
     }
-    // the state after the chunk: rows ti DR .. ti DR + DR - 1, columns 4 tj .. 4 tj + 3 (each thread owns its tile of Ss)
-    float sa[DR][4];
+    // the state after the chunk: rows ti DR .. ti DR + DR - 1, columns NV tj .. (each thread owns its tile of Ss)
+    float sa[DR][NV];
 #pragma unroll
     for (int x = 0; x < DR; ++x)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) sa[x][e] = 0.f;
+      for (int e = 0; e < NV; ++e) sa[x][e] = 0.f;
+#pragma unroll 2
     for (int j = 0; j < nt; ++j) {
       const float w = pw[nt - 1 - j];
-      float4 vv = f4(Vs + j * LDV + 4 * tj);
-      vv.x *= w; vv.y *= w; vv.z *= w; vv.w *= w;
+      float vv[NV];
+      ldv<NV>(Vs + j * LDV + NV * tj, vv);
+#pragma unroll
+      for (int e = 0; e < NV; ++e) vv[e] *= w;
       float kk[DR];
       if constexpr (DR % 4 == 0) {
 #pragma unroll
@@ -240,48 +266,50 @@ __global__ void __launch_bounds__(LA_T, 1) linear_attn_chunk_kernel(RecDev d, bo
         for (int x = 0; x < DR; ++x) kk[x] = Ks[j * LDQ + ti * DR + x];
       }
 #pragma unroll
-      for (int x = 0; x < DR; ++x) axpy4(sa[x], kk[x], vv);
+      for (int x = 0; x < DR; ++x) axpyv<NV>(sa[x], kk[x], vv);
     }
     const float wc = pw[nt];
 #pragma unroll
     for (int x = 0; x < DR; ++x) {
-      float* sr = Ss + (ti * DR + x) * LDV + 4 * tj;
-      float4 o = f4(sr);
-      o.x = fmaf(wc, o.x, sa[x][0]);
-      o.y = fmaf(wc, o.y, sa[x][1]);
-      o.z = fmaf(wc, o.z, sa[x][2]);
-      o.w = fmaf(wc, o.w, sa[x][3]);
-      *reinterpret_cast<float4*>(sr) = o;
+      float* sr = Ss + (ti * DR + x) * LDV + NV * tj;
+#pragma unroll
+      for (int e = 0; e < NV; ++e) sr[e] = fmaf(wc, sr[e], sa[x][e]);
     }
   }
   __syncthreads();
-  for (int e = t; e < DP * LA_VS; e += LA_T) {
-    const int i = e / LA_VS, c = e % LA_VS;
+  for (int e = t; e < DP * VS; e += LA_T) {
+    const int i = e / VS, c = e % VS;
     if (i < d.dim && v0 + c < d.vdim) sp[static_cast<long long>(i) * d.vdim + v0 + c] = Ss[i * LDV + c];
   }
 }
 
-template <int DP>
+template <int DP, int VS>
 static cudaError_t launch_la(const RecDev& d, int n_seqs, cudaStream_t st) {
-  constexpr size_t smem = sizeof(float) * LaSmem<DP>::floats;
+  constexpr size_t smem = sizeof(float) * LaSmem<DP, VS>::floats;
   static bool once = false;
   if (!once) {
-    cudaError_t e = cudaFuncSetAttribute(linear_attn_chunk_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(linear_attn_chunk_kernel<DP, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     once = true;
   }
   const auto al = [](const void* p, long long ld) { return reinterpret_cast<uintptr_t>(p) % 16 == 0 && ld % 4 == 0; };
   const bool vec = d.in_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.q, d.ldq) && al(d.k, d.ldk) && al(d.v, d.ldv);
-  return launch_kernel(linear_attn_chunk_kernel<DP>, dim3((d.vdim + LA_VS - 1) / LA_VS, d.heads, n_seqs), dim3(LA_T), smem, st, d, vec);
+  return launch_kernel(linear_attn_chunk_kernel<DP, VS>, dim3((d.vdim + VS - 1) / VS, d.heads, n_seqs), dim3(LA_T), smem, st, d, vec);
+}
+
+template <int DP>
+static cudaError_t launch_la_dp(const RecDev& d, int n_seqs, cudaStream_t st) {
+  // 64-column slices repeat the chunk's q k^T half as often; 32-column slices when those would leave SMs without a CTA
+  const long long ctas64 = static_cast<long long>((d.vdim + 63) / 64) * d.heads * n_seqs;
+  return ctas64 >= 148 ? launch_la<DP, 64>(d, n_seqs, st) : launch_la<DP, 32>(d, n_seqs, st);
 }
 
 cudaError_t launch_linear_attn_chunked(const RecDev& d, int n_seqs, cudaStream_t st) {
-  if (d.dim <= 16) return launch_la<16>(d, n_seqs, st);
-  if (d.dim <= 32) return launch_la<32>(d, n_seqs, st);
-  if (d.dim <= 64) return launch_la<64>(d, n_seqs, st);
-  return launch_la<128>(d, n_seqs, st);   // callers keep dim <= 128 here
+  if (d.dim <= 16) return launch_la_dp<16>(d, n_seqs, st);
+  if (d.dim <= 32) return launch_la_dp<32>(d, n_seqs, st);
+  if (d.dim <= 64) return launch_la_dp<64>(d, n_seqs, st);
+  return launch_la_dp<128>(d, n_seqs, st);   // callers keep dim <= 128 here
 }
-
 
 // ---- tiled windowed attention --------------------------------------------------------------------------------------------
 constexpr int WT_M = 64;            // queries per CTA

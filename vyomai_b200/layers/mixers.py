@@ -37,9 +37,9 @@ class Projection:
         if out is None:
             out = torch.empty((x.shape[0], _round_up(N, 8)), device=x.device, dtype=out_dtype)[:, :N]
         tc = self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and bias is None \
-            and act in (None, "none")
+            and act in (None, "none", "relu2")
         if tc:
-            ops.gemm(x, self.weight, addend=addend, out=out, out_scale=scale, swap_ab=x.shape[0] <= 32)
+            ops.gemm(x, self.weight, act=act, addend=addend, out=out, out_scale=scale, swap_ab=x.shape[0] <= 32)
         else:
             ops.linear_plain(x, self.weight, bias=bias, act=act, scale=scale, addend=addend, out=out)
         return out
@@ -191,9 +191,5 @@ class ReluSquaredMLP:
         self.act_dtype = act_dtype
 
     def forward(self, h: torch.Tensor, x_residual: torch.Tensor) -> torch.Tensor:
-        if self.up.tensor_cores and h.dtype == torch.bfloat16:
-            z = self.up(h)                                   # fp32 pre-activation off the tensor cores
-            u = ops.unary(z, "relu2", self.act_dtype)        # squared in fp32, rounded once
-        else:
-            u = self.up(h, act="relu2", out_dtype=self.act_dtype)
+        u = self.up(h, act="relu2", out_dtype=self.act_dtype)   # squared on the fp32 accumulator in the epilogue, rounded once
         return self.down(u, addend=x_residual, out=x_residual)

@@ -28,6 +28,7 @@ ACT = {
     "geglu_tanh": C["VY_ACT_GEGLU_TANH"],
     "gelu_erf": C["VY_ACT_GELU_ERF"],
     "gelu_tanh": C["VY_ACT_GELU_TANH"],
+    "relu2": C["VY_ACT_RELU2"],
     "dgelu": C["VY_ACT_DGELU_ERF"],
     "dgelu_erf": C["VY_ACT_DGELU_ERF"],
     "dgelu_tanh": C["VY_ACT_DGELU_TANH"],
