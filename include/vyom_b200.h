@@ -760,8 +760,13 @@ typedef struct VyDeltaRule {
   float unit_eps;
   float* state;
   void* out; int64_t ld_out; int32_t out_dtype;
+  /* optional: with a workspace of at least vy_delta_rule_workspace_floats(rows, heads, kv_heads, dim) floats (rows = token rows of
+   * the step), the unit vectors, decays and write strengths of all tokens are computed by one parallel launch before the
+   * token-serial kernel instead of inside it */
+  int64_t rows; float* workspace; int64_t workspace_floats;
   void* stream;
 } VyDeltaRule;
+VY_API int64_t vy_delta_rule_workspace_floats(int64_t rows, int32_t heads, int32_t kv_heads, int32_t dim);
 VY_API int vy_delta_rule(const VyDeltaRule* p);
 
 

@@ -267,3 +267,89 @@ def test_delta_rule_overwrites_a_key_it_has_seen():
         S = S + torch.outer(kk[t], v[t].double() - S.T @ kk[t])
     assert rel_err(out[2], (S.T @ kk[2]) / math.sqrt(dk)) < 1e-4
     assert rel_err(out[2] * math.sqrt(dk), v[2]) < 0.2      # close to v2 alone (k_1 is nearly orthogonal), far from v1 + v2
+
+
+# ---- the prompt-sized (tiled / chunked) forms against the token-serial ones: sizes at their switch-over points and tile edges ----
+@pytest.mark.parametrize("dk,dv", [(128, 128), (10, 6), (64, 200)])
+def test_window_attention_tile_edges_and_head_sizes(dk, dv):
+    """Portions of 15 / 16 tokens sit on either side of the switch to the tiled kernel; 64 / 65 / 130 on either side of its query
+    tile; window 70 makes the band start inside a key tile; head sizes with and without 16-byte rows."""
+    ops = _ops()
+    H, G, scale, window, keep, T = 4, 2, 0.2, 70, 3, 230
+    spikes = [(0, 229, 2, 0), (0, 229, 3, 1), (0, 229, 229 - 69, 2), (0, 229, 229 - 70, 3), (0, 128, 128 - 69, 0), (0, 64, 0, 1)]
+    q, k, v, gate = _attention_case([T, 37], H, G, dk, dv, 12, spikes)
+    sink = torch.tensor([0.5, -2.0, 1.0, 0.0])
+    ref = [O.window_sink_attention(q[s].double(), k[s].double(), v[s].double(), scale=scale, window=window, keep_first=keep, sink=sink.double(),
+                                   gate_logits=gate[s].double()).reshape(len(q[s]), -1) for s in range(2)]
+    for cuts in ([[230], [37]], [[15, 16, 64, 65, 70], [16, 15, 6]], [[130, 99, 1], [1, 36]]):
+        got = _attend(ops, q, k, v, [T, 37], cuts, H=H, G=G, dk=dk, dv=dv, scale=scale, window=window, keep=keep, sink=sink, gate=gate, bs=16)
+        for s in range(2):
+            assert rel_err(got[s], ref[s]) < 1e-4, (cuts, s)
+
+
+@pytest.mark.parametrize("H,dk,dv", [(2, 128, 128), (1, 20, 70)])
+def test_linear_attention_chunk_edges(H, dk, dv):
+    """Portions of 7 / 8 tokens on either side of the switch to the chunked kernel, 64 / 65 / 129 around its chunk, and value widths
+    that need one, two and three column slices."""
+    ops = _ops()
+    lengths = [200, 9]
+    g = torch.Generator().manual_seed(13)
+    mk = lambda d: [torch.randn(L, H * d, generator=g) for L in lengths]  # noqa: E731
+    q, k, v = mk(dk), mk(dk), mk(dv)
+    decay = [0.8, 0.9991][:H]
+    ref = [O.lightning_attention(O.silu(q[s].double()).view(-1, H, dk), O.silu(k[s].double()).view(-1, H, dk), O.silu(v[s].double()).view(-1, H, dv),
+                                 decay).reshape(lengths[s], -1) for s in range(2)]
+    dec = torch.tensor(decay, device=DEV)
+    for cuts in ([[200], [9]], [[7, 8, 64, 65, 56], [8, 1]], [[129, 70, 1], [2, 7]]):
+        got = _recur(lambda b, cat, st: ops.linear_attn(b, cat("q"), cat("k"), cat("v"), dec, st[0], heads=H, dim=dk, vdim=dv, in_act="silu"),
+                     lengths, cuts, {"q": q, "k": k, "v": v}, [(H, dk, dv)])
+        for s in range(2):
+            assert rel_err(got[s], ref[s]) < 2e-4, (cuts, s)
+
+
+@pytest.mark.parametrize("H,G,dk,dv", [(2, 1, 128, 128), (1, 1, 200, 40)])
+def test_gated_delta_rule_wide_heads(H, G, dk, dv):
+    ops = _ops()
+    lengths = [50, 3]
+    g = torch.Generator().manual_seed(14)
+    mk = lambda d: [torch.randn(L, d, generator=g) for L in lengths]  # noqa: E731
+    q, k, v, a, b = mk(G * dk), mk(G * dk), mk(H * dv), mk(H * dk), mk(H)
+    a_log = torch.randn(H, generator=g) * 0.5 - 1.0
+    ref = []
+    for s in range(2):
+        L = lengths[s]
+        qq = O.unit(q[s].double().view(L, G, dk)) * dk ** -0.5
+        kk = O.unit(k[s].double().view(L, G, dk))
+        gg = torch.exp(-torch.exp(a_log.double())[None, :, None] * torch.nn.functional.softplus(a[s].double()).view(L, H, dk))
+        ref.append(O.gated_delta_rule(qq, kk, v[s].double().view(L, H, dv), gg, torch.sigmoid(b[s].double())).reshape(L, -1))
+    for cuts in ([[50], [3]], [[17, 16, 1, 15], [1, 2]]):
+        got = _recur(lambda bt, cat, st: ops.delta_rule(bt, cat("q"), cat("k"), cat("v"), cat("a"), cat("b"), a_log.to(DEV), st[0], heads=H,
+                                                        kv_heads=G, dim=dk, vdim=dv, unit_eps=1e-6),
+                     lengths, cuts, {"q": q, "k": k, "v": v, "a": a, "b": b}, [(H, dk, dv)])
+        for s in range(2):
+            assert rel_err(got[s], ref[s]) < 1e-4, (cuts, s)
+
+
+@pytest.mark.parametrize("rows,width", [(3, 1024), (70, 300), (5, 2048), (2, 2500)])
+def test_rms_norm_row_widths(rows, width):
+    """Widths served by each thread layout (a warp, 128 and 256 threads per row, and the re-reading kernel above 2048)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(15)
+    x = torch.randn(rows, width, generator=g) * 2
+    w = torch.randn(width, generator=g) * 0.2
+    gate = torch.randn(rows, width, generator=g)
+    ref = O.rms(x.double(), 1e-6) * (1 + w.double()) * torch.sigmoid(gate.double())
+    got = ops.rms_norm(x.to(DEV), w.to(DEV), eps=1e-6, w_mode="one_plus", gate=gate.to(DEV), gate_act="sigmoid")
+    assert rel_err(got.cpu(), ref) < 1e-5
+
+
+def test_squared_relu_in_the_projection_epilogue():
+    """bf16 inputs on the tensor-core path, prompt-sized and single-token-sized: the activation is applied to the fp32 accumulator."""
+    from vyomai_b200.layers.mixers import Projection
+    g = torch.Generator().manual_seed(16)
+    w = (torch.randn(96, 64, generator=g) / 8).bfloat16()
+    for rows in (3, 200):
+        x = torch.randn(rows, 64, generator=g).bfloat16()
+        got = Projection(w.to(DEV))(x.to(DEV), act="relu2", out_dtype=torch.float32)
+        ref = torch.relu(x.double() @ w.double().T) ** 2
+        assert rel_err(got.cpu(), ref) < 1e-5

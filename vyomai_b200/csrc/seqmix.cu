@@ -537,13 +537,13 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
       const int e = threadIdx.x + u * 128, tt = e / DP, i = e - tt * DP;
       qs[tt][i] = rq[u];
       ks[tt][i] = rk[u];
-      gs[tt][i] = ra[u] == -INFINITY ? 1.f : expf(neg_rate * softplusf_(ra[u]));
+      gs[tt][i] = ra[u] == -INFINITY ? 1.f : (d.prepared ? ra[u] : expf(neg_rate * softplusf_(ra[u])));
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) vs[threadIdx.x + u * 128] = rv[u];
-    if (threadIdx.x < nt) betas[threadIdx.x] = sigmoidf_(rb);
+    if (threadIdx.x < nt) betas[threadIdx.x] = d.prepared ? rb : sigmoidf_(rb);
     __syncthreads();
-    for (int tt = warp; tt < nt; tt += nwarps) {
+    for (int tt = d.prepared ? nt : warp; tt < nt; tt += nwarps) {
       float sq = 0.f, sk = 0.f;
       for (int i = lane; i < DP; i += 32) {
         sq = fmaf(qs[tt][i], qs[tt][i], sq);
@@ -605,6 +605,51 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
         const int i = 16 * m + 4 * part + e;
         if (i < d.dim) sp[static_cast<long long>(i) * d.vdim] = S[m][e];
       }
+  }
+}
+
+// the delta rule's per-token inputs, all tokens in parallel: one warp per (token, head) writes the head's decays and write strength,
+// and for the first head of each q / k group the group's unit vectors (q also times dim^-1/2)
+struct DeltaPrepDev {
+  long long rows;
+  const void* q; long long ldq; const void* k; long long ldk; int in_dt;
+  const void* a; long long ld_a; int a_dt;
+  const void* b; long long ld_b; int b_dt;
+  const void* a_log; int a_log_dt;
+  int heads, kv_heads, dim;
+  float unit_eps;
+  float* qn; float* kn; float* g; float* beta;
+};
+
+__global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepDev d) {
+  pdl_trigger();
+  pdl_wait();
+  const long long w = blockIdx.x * 4LL + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= d.rows * d.heads) return;
+  const long long tok = w / d.heads;
+  const int h = static_cast<int>(w - tok * d.heads);
+  const float neg_rate = -expf(ld_as_float(d.a_log, d.a_log_dt, h));
+  for (int i = lane; i < d.dim; i += 32)
+    d.g[(tok * d.heads + h) * d.dim + i] = expf(neg_rate * softplusf_(ld_as_float(d.a, d.a_dt, tok * d.ld_a + static_cast<long long>(h) * d.dim + i)));
+  if (lane == 0) d.beta[tok * d.heads + h] = sigmoidf_(ld_as_float(d.b, d.b_dt, tok * d.ld_b + h));
+  const int rep = d.heads / d.kv_heads;
+  if (h % rep) return;
+  const int gq = h / rep;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < d.dim; i += 32) {
+    const float qv = ld_as_float(d.q, d.in_dt, tok * d.ldq + static_cast<long long>(gq) * d.dim + i);
+    const float kv = ld_as_float(d.k, d.in_dt, tok * d.ldk + static_cast<long long>(gq) * d.dim + i);
+    sq = fmaf(qv, qv, sq);
+    sk = fmaf(kv, kv, sk);
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  const float qn = 1.f / sqrtf(static_cast<float>(d.dim)) / sqrtf(sq + d.unit_eps), kn = 1.f / sqrtf(sk + d.unit_eps);
+  for (int i = lane; i < d.dim; i += 32) {
+    const long long o = (tok * d.kv_heads + gq) * d.dim + i;
+    d.qn[o] = ld_as_float(d.q, d.in_dt, tok * d.ldq + static_cast<long long>(gq) * d.dim + i) * qn;
+    d.kn[o] = ld_as_float(d.k, d.in_dt, tok * d.ldk + static_cast<long long>(gq) * d.dim + i) * kn;
   }
 }
 
@@ -789,6 +834,10 @@ extern "C" int vy_linear_attn(const VyLinAttn* p) {
   return VY_OK;
 }
 
+extern "C" int64_t vy_delta_rule_workspace_floats(int64_t rows, int32_t heads, int32_t kv_heads, int32_t dim) {
+  return rows * (2LL * kv_heads * dim + static_cast<int64_t>(heads) * dim + heads);
+}
+
 extern "C" int vy_delta_rule(const VyDeltaRule* p) {
   using namespace vy;
   VY_CHECK_ARG(p != nullptr, "vy_delta_rule: null params");
@@ -808,8 +857,28 @@ extern "C" int vy_delta_rule(const VyDeltaRule* p) {
   d.heads = p->heads; d.kv_heads = p->kv_heads; d.dim = p->dim; d.vdim = p->vdim;
   d.unit_eps = p->unit_eps;
   d.state = p->state;
-  d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
+  if (p->workspace && p->rows > 0 && p->in_dtype == VY_F32 && p->workspace_floats >= vy_delta_rule_workspace_floats(p->rows, p->heads, p->kv_heads, p->dim)) {
+    DeltaPrepDev pd;
+    pd.rows = p->rows;
+    pd.q = p->q; pd.ldq = p->ldq; pd.k = p->k; pd.ldk = p->ldk; pd.in_dt = p->in_dtype;
+    pd.a = p->a; pd.ld_a = p->ld_a; pd.a_dt = p->a_dtype;
+    pd.b = p->b; pd.ld_b = p->ld_b; pd.b_dt = p->b_dtype;
+    pd.a_log = p->a_log; pd.a_log_dt = p->a_log_dtype;
+    pd.heads = p->heads; pd.kv_heads = p->kv_heads; pd.dim = p->dim; pd.unit_eps = p->unit_eps;
+    const long long qk = p->rows * p->kv_heads * p->dim, hg = p->rows * p->heads * p->dim;
+    pd.qn = p->workspace; pd.kn = pd.qn + qk; pd.g = pd.kn + qk; pd.beta = pd.g + hg;
+    const long long blocks = (p->rows * p->heads + 3) / 4;
+    VY_CHECK_ARG(blocks <= 2147483647LL, "vy_delta_rule: too many rows");
+    VY_CUDA_OK(launch_kernel(delta_prep_kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 0, st, pd));
+    VY_LAUNCH_OK();
+    count_launch();
+    d.q = pd.qn; d.ldq = static_cast<long long>(p->kv_heads) * p->dim; d.k = pd.kn; d.ldk = d.ldq; 
+    d.a = pd.g; d.ld_a = static_cast<long long>(p->heads) * p->dim; d.a_dt = VY_F32;
+    d.b = pd.beta; d.ld_b = p->heads; d.b_dt = VY_F32;
+    d.prepared = 1;
+  }
+  d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   cudaError_t e;
   switch (pad_dim(p->dim)) {
     case 16: e = launch_delta_rule<16>(d, p->n_seqs, st); break;

@@ -51,6 +51,7 @@ struct RecDev {
   const float* decay;
   int heads, kv_heads, dim, vdim;
   float unit_eps;
+  int prepared;   // delta rule: q / k are unit vectors already (q scaled), `a` holds the decays and `b` the write strengths
   float* state;
   void* out; long long ld_out; int out_dt;
 };

@@ -1032,7 +1032,9 @@ def delta_rule(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Te
     if state.dtype != torch.float32 or not state.is_contiguous():
         raise _lib.VyomError("delta_rule: state is fp32")
     out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or torch.float32)
-    _lib.call("vy_delta_rule", "VyDeltaRule", q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
+    rows = q.shape[0]
+    ws = torch.empty(rows * (2 * kv_heads * dim + heads * dim + heads), device=q.device, dtype=torch.float32)   # unit q / k, decays, strengths
+    _lib.call("vy_delta_rule", "VyDeltaRule", rows=rows, workspace=ws.data_ptr(), workspace_floats=ws.numel(), q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
               in_dtype=_dt(q), a=a.data_ptr(), ld_a=a.stride(0), a_dtype=_dt(a), b=b.data_ptr(), ld_b=b.stride(0), b_dtype=_dt(b),
               a_log=a_log.data_ptr(), a_log_dtype=_dt(a_log), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, unit_eps=float(unit_eps),
               state=state.data_ptr(), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw())
