@@ -471,15 +471,20 @@ __global__ void __launch_bounds__(128) linear_attn_kernel(RecDev d) {
   }
 }
 
-// gated delta rule: a column of the state is shared by 4 adjacent lanes, lane `part` holding channels 16 m + 4 part .. + 3 of
-// every group of 16 (so the chunk's k / q / decay rows are read as one float4 per group and a warp touches 64 contiguous bytes);
-// the two contractions over the channels end in two shuffles each
+// gated delta rule: a column of the state is shared by LANES adjacent lanes, lane `part` holding channels 4 LANES m + 4 part .. + 3
+// of every group of 4 LANES (so the chunk's k / q / decay rows are read as one float4 per group, contiguous across the lanes); the
+// two contractions over the channels end in log2(LANES) shuffles each. A CTA owns 32 columns: the recurrence is a dependent chain
+// per token, so the lanes per column (not the work per lane) set how many warps there are to overlap those chains
 template <int DP>
-__global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
+struct DeltaLanes { static constexpr int value = DP >= 32 ? 8 : 4; };
+
+template <int DP>
+__global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(RecDev d) {
   pdl_trigger();
   pdl_wait();
   constexpr int CT = RecChunk<DP>::CT;
-  constexpr int NM = DP / 16;
+  constexpr int LANES = DeltaLanes<DP>::value, T = 32 * LANES;
+  constexpr int NM = DP / (4 * LANES);
   extern __shared__ __align__(16) float dr_smem[];
   float (*qs)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem);
   float (*ks)[DP] = reinterpret_cast<float (*)[DP]>(dr_smem + CT * DP);
@@ -487,9 +492,9 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
   float* betas = dr_smem + 3 * CT * DP;
   float* vs = betas + CT;                       // [CT][32]: the chunk's values of this CTA's 32 columns
   const int s = blockIdx.z, h = blockIdx.y;
-  const int part = threadIdx.x & 3;
-  const int j = blockIdx.x * 32 + (threadIdx.x >> 2);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int part = threadIdx.x & (LANES - 1), col = threadIdx.x / LANES;
+  const int j = blockIdx.x * 32 + col;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
   if (n <= 0) return;
   const bool active = j < d.vdim;
@@ -503,18 +508,18 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
   for (int m = 0; m < NM; ++m)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int i = 16 * m + 4 * part + e;
+      const int i = 4 * LANES * m + 4 * part + e;
       S[m][e] = (carried && active && i < d.dim) ? sp[static_cast<long long>(i) * d.vdim] : 0.f;
     }
   // the next chunk's raw q / k / decay inputs travel in registers while the current chunk is walked
-  constexpr int NPF = CT * DP / 128;
-  constexpr int NV = CT * 32 / 128;
+  constexpr int NPF = CT * DP / T;
+  constexpr int NV = CT * 32 / T;
   float rq[NPF], rk[NPF], ra[NPF], rv[NV], rb = 0.f;
   auto fetch = [&](int t0) {
     const int nt = min(CT, n - t0);
 #pragma unroll
     for (int u = 0; u < NPF; ++u) {
-      const int e = threadIdx.x + u * 128, tt = e / DP, i = e - tt * DP;
+      const int e = threadIdx.x + u * T, tt = e / DP, i = e - tt * DP;
       const bool ok = tt < nt && i < d.dim;
       const long long row = base + t0 + tt;
       rq[u] = ok ? ld_as_float(d.q, d.in_dt, row * d.ldq + static_cast<long long>(gq) * d.dim + i) : 0.f;
@@ -523,7 +528,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
-      const int e = threadIdx.x + u * 128, tt = e >> 5, c = static_cast<int>(blockIdx.x) * 32 + (e & 31);
+      const int e = threadIdx.x + u * T, tt = e >> 5, c = static_cast<int>(blockIdx.x) * 32 + (e & 31);
       rv[u] = (tt < nt && c < d.vdim) ? ld_as_float(d.v, d.in_dt, static_cast<long long>(base + t0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + c) : 0.f;
     }
     if (threadIdx.x < nt) rb = ld_as_float(d.b, d.b_dt, static_cast<long long>(base + t0 + threadIdx.x) * d.ld_b + h);
@@ -534,13 +539,13 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     __syncthreads();
 #pragma unroll
     for (int u = 0; u < NPF; ++u) {
-      const int e = threadIdx.x + u * 128, tt = e / DP, i = e - tt * DP;
+      const int e = threadIdx.x + u * T, tt = e / DP, i = e - tt * DP;
       qs[tt][i] = rq[u];
       ks[tt][i] = rk[u];
       gs[tt][i] = ra[u] == -INFINITY ? 1.f : (d.prepared ? ra[u] : expf(neg_rate * softplusf_(ra[u])));
     }
 #pragma unroll
-    for (int u = 0; u < NV; ++u) vs[threadIdx.x + u * 128] = rv[u];
+    for (int u = 0; u < NV; ++u) vs[threadIdx.x + u * T] = rv[u];
     if (threadIdx.x < nt) betas[threadIdx.x] = d.prepared ? rb : sigmoidf_(rb);
     __syncthreads();
     for (int tt = d.prepared ? nt : warp; tt < nt; tt += nwarps) {
@@ -561,13 +566,13 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     if (t0 + CT < n) fetch(t0 + CT);
     for (int tt = 0; tt < nt; ++tt) {
       const long long row = base + t0 + tt;
-      const float vj = vs[tt * 32 + (threadIdx.x >> 2)];
+      const float vj = vs[tt * 32 + col];
       float4 k4[NM];
       float r0 = 0.f, r1 = 0.f;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
-        const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][16 * m + 4 * part]);
-        k4[m] = *reinterpret_cast<const float4*>(&ks[tt][16 * m + 4 * part]);
+        const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][4 * LANES * m + 4 * part]);
+        k4[m] = *reinterpret_cast<const float4*>(&ks[tt][4 * LANES * m + 4 * part]);
         S[m][0] *= g4.x; S[m][1] *= g4.y; S[m][2] *= g4.z; S[m][3] *= g4.w;
         r0 = fmaf(S[m][0], k4[m].x, r0);
         r1 = fmaf(S[m][1], k4[m].y, r1);
@@ -575,13 +580,13 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
         r1 = fmaf(S[m][3], k4[m].w, r1);
       }
       float r = r0 + r1;
-      r += __shfl_xor_sync(0xffffffffu, r, 1);
-      r += __shfl_xor_sync(0xffffffffu, r, 2);
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
       const float u = betas[tt] * (vj - r);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
-        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][16 * m + 4 * part]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][4 * LANES * m + 4 * part]);
         S[m][0] = fmaf(k4[m].x, u, S[m][0]);
         S[m][1] = fmaf(k4[m].y, u, S[m][1]);
         S[m][2] = fmaf(k4[m].z, u, S[m][2]);
@@ -592,8 +597,8 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
         o1 = fmaf(S[m][3], q4.w, o1);
       }
       float o = o0 + o1;
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+      for (int x = 1; x < LANES; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
       if (active && part == 0) st_from_float(d.out, d.out_dt, row * d.ld_out + static_cast<long long>(h) * d.vdim + j, o);
     }
   }
@@ -602,7 +607,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(RecDev d) {
     for (int m = 0; m < NM; ++m)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = 16 * m + 4 * part + e;
+        const int i = 4 * LANES * m + 4 * part + e;
         if (i < d.dim) sp[static_cast<long long>(i) * d.vdim] = S[m][e];
       }
   }
@@ -792,10 +797,10 @@ static cudaError_t launch_linear_attn(const RecDev& d, int n_seqs, cudaStream_t 
 }
 template <int DP>
 static cudaError_t launch_delta_rule(const RecDev& d, int n_seqs, cudaStream_t st) {
-  const int threads = 128;   // 4 lanes per state column, 32 columns per CTA
+  const int threads = 32 * DeltaLanes<DP>::value;   // 32 state columns per CTA
   constexpr int CT = RecChunk<DP>::CT;
   const size_t smem = sizeof(float) * (3 * CT * DP + CT + CT * 32);
-  const int cols = threads / 4;
+  const int cols = 32;
   return launch_kernel(delta_rule_kernel<DP>, dim3((d.vdim + cols - 1) / cols, d.heads, n_seqs), dim3(threads), smem, st, d);
 }
 }  // namespace vy
