@@ -977,6 +977,22 @@ def measure_hybrid(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, de
     pre_ms = sorted(times)[len(times) // 2]
     out["prefill"] = {"batch": batch_prefill, "prompt": prompt, "ms": round(pre_ms, 3), "tok_per_s": round(batch_prefill * prompt / pre_ms * 1e3)}
     out["prefill_kernels"] = _kernel_table(lambda: prefill(batch_prefill))
+    # the three sequence mixers are fp32 by definition (scores, weights, state): their roofline is the FMA rate, not the tensor cores'
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    fp32_tflops = sms * 128 * 2 * 1.965e9 / 1e12          # nominal: 128 FMA lanes per SM at the maximum SM clock
+    tokens, lin, par = batch_prefill * prompt, cfgd["layers"][0]["mixer"], cfgd["layers"][3]["mixer"]
+    n_lin = sum(1 for L in cfgd["layers"] if L["type"] == "lightning")
+    n_par = len(cfgd["layers"]) - n_lin
+    W, K = par["left"]["mask"]["size"], par["left"]["mask"]["keep_first"]
+    visible = sum(min(p + 1, W) + (min(K, p + 1 - W) if p + 1 > W else 0) for p in range(prompt)) / prompt
+    flops = {"linear_attn_chunk": n_lin * tokens * lin["heads"] * (2 * lin["dim"] * lin["vdim"] + 32 * (lin["dim"] + lin["vdim"])) * 2,
+             "window_attn": n_par * tokens * par["left"]["heads"] * visible * (par["left"]["dim"] + par["left"]["vdim"]) * 2,
+             "delta_rule": n_par * tokens * par["right"]["heads"] * 3 * par["right"]["dim"] * par["right"]["vdim"] * 2}
+    out["prefill_fp32_roofline"] = {"fp32_tflops_nominal": round(fp32_tflops, 1)}
+    for name, f in flops.items():
+        ms = out["prefill_kernels"].get(name, {}).get("ms")
+        if ms:
+            out["prefill_fp32_roofline"][name] = {"gflop": round(f / 1e9, 1), "tflops": round(f / ms / 1e9, 2), "frac": round(f / ms / 1e9 / fp32_tflops, 3)}
     eng.release(range(batch_prefill))
 
     # decode: batch_decode sequences at context `prompt`, one token each per step (second step captures the graph)

@@ -297,7 +297,7 @@ __device__ __forceinline__ void epilogue_linear_general(const GemmDev& g, uint32
 enum { EPI_PLAIN = 0, EPI_ADD = 1, EPI_GELU = 2, EPI_DGELU = 3 };
 //   EPI_PLAIN  out = scale * (acc + bias)
 //   EPI_ADD    out = scale * (acc + bias + addend)                   (residual add / gradient accumulation)
-//   EPI_GELU   aux = acc + bias (if aux);  out = scale * gelu_erf(acc + bias)
+//   EPI_GELU   aux = acc + bias (if aux);  out = scale * gelu_erf(acc + bias)      (act RELU2: max(acc + bias, 0)^2 instead)
 //   EPI_DGELU  out = scale * (acc + bias) * gelu_erf'(aux)
 // Software pipeline per warp: the tcgen05.ld of chunk c+1 is in flight while chunk c is processed; the
 // row operand (addend / aux) of the first two chunks is fetched before the accumulator is awaited and
@@ -433,8 +433,13 @@ __device__ __forceinline__ void epilogue_linear_fast(const GemmDev& g, uint32_t 
         if (save_aux)
           *reinterpret_cast<uint4*>(stage + GEMM_STAGE_OUT + lane * 64 + ((j4 ^ sw) << 4)) =
               make_uint4(pack2_bf16(x[0], x[1]), pack2_bf16(x[2], x[3]), pack2_bf16(x[4], x[5]), pack2_bf16(x[6], x[7]));
+        if (g.act == VY_ACT_RELU2) {   // the same fast path serves the squared ReLU
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = gelu_erf(x[j]);
+          for (int j = 0; j < 8; ++j) { const float r = fmaxf(x[j], 0.f); x[j] = r * r; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = gelu_erf(x[j]);
+        }
       } else if (MODE == EPI_DGELU) {
         float z[8];
         unpack8_bf16(pc[j4], z);
@@ -1022,7 +1027,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const bool aux16 = !g.aux || g.aux_dtype == VY_BF16;
       const bool n8 = (g.N & 7) == 0;  // the prefetched row operand is read in 8-column vectors
       if (g.act == VY_ACT_NONE) fast_mode = !g.addend ? EPI_PLAIN : ((g.addend_dtype == VY_BF16 && n8) ? EPI_ADD : -1);
-      else if (g.act == VY_ACT_GELU_ERF && !g.addend && aux16) fast_mode = EPI_GELU;
+      else if ((g.act == VY_ACT_GELU_ERF || g.act == VY_ACT_RELU2) && !g.addend && aux16) fast_mode = EPI_GELU;
       else if (g.act == VY_ACT_DGELU_ERF && !g.addend && aux16 && n8) fast_mode = EPI_DGELU;
     }
     uint32_t local = 0;

@@ -154,12 +154,17 @@ __global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kern
                          [&](int tt) { return tt < nt ? (r0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + v0 : -1LL; });
     }
     __syncthreads();
-    // what the earlier chunks left: oi[r][e] = sum_i Q[ti + 16 r][i] S0[i][NV tj + e]
-    float oi[4][NV];
+    // one pass over the channels feeds both contractions that read the chunk's queries:
+    //   what the earlier chunks left, oi[r][e] = sum_i Q[ti + 16 r][i] S0[i][NV tj + e], and
+    //   the weights inside the chunk, P[i][j] = (q_i . k_j) decay^(i-j) for j <= i (rows ti + 16 r, columns tj + 16 c, blocks c <= r)
+    float oi[4][NV], p[4][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
+    for (int r = 0; r < 4; ++r) {
 #pragma unroll
       for (int e = 0; e < NV; ++e) oi[r][e] = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) p[r][c] = 0.f;
+    }
 #pragma unroll 2
     for (int d4 = 0; d4 < DP; d4 += 4) {
       float s0[NV], s1[NV], s2[NV], s3[NV];
@@ -167,6 +172,9 @@ __global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kern
       ldv<NV>(Ss + (d4 + 1) * LDV + NV * tj, s1);
       ldv<NV>(Ss + (d4 + 2) * LDV + NV * tj, s2);
       ldv<NV>(Ss + (d4 + 3) * LDV + NV * tj, s3);
+      float4 kv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kv[c] = f4(Ks + (tj + 16 * c) * LDQ + d4);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float4 qv = f4(Qs + (ti + 16 * r) * LDQ + d4);
@@ -174,22 +182,6 @@ __global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kern
         axpyv<NV>(oi[r], qv.y, s1);
         axpyv<NV>(oi[r], qv.z, s2);
         axpyv<NV>(oi[r], qv.w, s3);
-      }
-    }
-    // weights inside the chunk: P[i][j] = (q_i . k_j) decay^(i-j) for j <= i; rows ti + 16 r, columns tj + 16 c, blocks c <= r
-    float p[4][4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) p[r][c] = 0.f;
-#pragma unroll 2
-    for (int d4 = 0; d4 < DP; d4 += 4) {
-      float4 kv[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) kv[c] = f4(Ks + (tj + 16 * c) * LDQ + d4);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const float4 qv = f4(Qs + (ti + 16 * r) * LDQ + d4);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           if (c <= r) p[r][c] = dot4(qv, kv[c], p[r][c]);
