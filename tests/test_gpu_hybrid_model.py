@@ -140,6 +140,21 @@ def test_other_sizes(seed, layers, width, vocab):
         assert U.rel_err(U.feed_in_portions(eng, "s", toks, [21, 2]), ref) < TOL[dtype]
 
 
+def test_wide_heads_and_a_prompt_longer_than_a_tile():
+    """128-wide heads (the kernels' 16-byte load paths and widest templates), a 150-token prompt fed as 70 + 2 + 65 and the rest decoded,
+    window 40 with 2 kept tokens: the prompt crosses the tiled kernels' 64-token tiles and chunks inside and between portions."""
+    layers = [U.lightning(heads=2, dim=128, vdim=128, decay=(0.9, 0.999), ff=128),
+              U.parallel(heads=2, kv_heads=1, dim=128, vdim=128, window=40, keep_first=2, scale=0.09, r_heads=2, r_kv=1, r_dim=128, r_vdim=128,
+                         taps=4, ff=128)]
+    cfg = U.config(layers, width=256, vocab=300, eps=1e-6, emb_scale=1.0, logit_scale=0.5)
+    for dtype in (torch.float32, torch.bfloat16):
+        model, W = U.build(cfg, dtype=dtype, seed=7, ranks=(8, 8))
+        eng, _ = U.engine_for(model, block_size=16)
+        toks = U.tokens(150, 300, 8)
+        ref = _oracle_logits(cfg, W, toks)
+        assert U.rel_err(U.feed_in_portions(eng, "s", toks, [70, 2, 65]), ref) < TOL[dtype]
+
+
 def test_greedy_generation_through_the_engine():
     """generate(): waiting room (batch limit 2 for 3 prompts), prompts and decoding tokens in the same packed step. Tokens must
     equal the oracle's greedy continuation wherever its top-1 / top-2 margin is not at rounding level."""
