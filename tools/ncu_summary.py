@@ -57,7 +57,7 @@ def fmt(uv):
 def main():
     dst, reps = sys.argv[1], sys.argv[2:]
     lines = ["# ncu --set full summaries", "",
-             "Captured under gpurun with `--clock-control none --import-source on`; durations are cold-cache, serialised "
+             "Captured under gpurun with `--clock-control none`; durations are cold-cache, serialised "
              "(never bench values). Raw reports stay in gpurun_out/ (scratch).", ""]
     for rep in reps:
         for k in load(rep):
