@@ -62,11 +62,11 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
   constexpr int NC = 8, RPB = 256 / TPR;
   __shared__ float part[RPB][TPR / 32 + 1];
   const int lr = threadIdx.x / TPR, lt = threadIdx.x % TPR;
-  const long long r = blockIdx.x * static_cast<long long>(RPB) + lr;
-  const bool live = r < d.rows;
-  const long long tok = live ? r / d.groups : 0;
-  const int grp = live ? static_cast<int>(r - tok * d.groups) : 0;
-  const long long st = d.row_index ? d.row_index[tok] : tok;
+  const unsigned r = blockIdx.x * static_cast<unsigned>(RPB) + lr;   // the launcher keeps rows below 2^31: 32-bit division
+  const bool live = r < static_cast<unsigned>(d.rows);
+  const unsigned tok = live ? (d.groups == 1 ? r : r / static_cast<unsigned>(d.groups)) : 0u;
+  const int grp = live ? static_cast<int>(r - tok * static_cast<unsigned>(d.groups)) : 0;
+  const long long st = d.row_index ? d.row_index[tok] : static_cast<long long>(tok);
   const long long xo = st * d.ldx + static_cast<long long>(grp) * d.width;
   float xv[NC];
   float ss = 0.f;
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
   if (!live) return;
   const float inv = d.coef / sqrtf(ss / static_cast<float>(d.width) + d.eps);
   const long long go = st * d.ld_gate + static_cast<long long>(grp) * d.width;
-  const long long oo = tok * d.ld_out + static_cast<long long>(grp) * d.width;
+  const long long oo = static_cast<long long>(tok) * d.ld_out + static_cast<long long>(grp) * d.width;
 #pragma unroll
   for (int i = 0; i < NC; ++i) {
     const int c = lt + i * TPR;
@@ -688,7 +688,7 @@ extern "C" int vy_rms_norm(const VyRmsNorm* p) {
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   const int tpr = d.width <= 256 ? 32 : d.width <= 1024 ? 128 : d.width <= 2048 ? 256 : 0;
   const long long blocks = tpr ? (d.rows + 256 / tpr - 1) / (256 / tpr) : (d.rows + 3) / 4;
-  VY_CHECK_ARG(blocks <= 2147483647LL, "vy_rms_norm: too many rows");
+  VY_CHECK_ARG(blocks <= 2147483647LL && d.rows <= 2147483647LL, "vy_rms_norm: too many rows");
   const dim3 grid(static_cast<unsigned>(blocks));
   if (tpr == 32) VY_CUDA_OK(launch_kernel(rms_norm_cached_kernel<32>, grid, dim3(256), 0, st, d));
   else if (tpr == 128) VY_CUDA_OK(launch_kernel(rms_norm_cached_kernel<128>, grid, dim3(256), 0, st, d));

@@ -9,6 +9,8 @@
 //     the visible keys in tiles of 64 (the kept prefix first, then the window band) with an online softmax.
 //
 // Both give the same values as the token-serial kernels of seqmix.cu up to fp32 rounding, whatever the portion sizes.
+#include <stdlib.h>
+
 #include "seqmix.cuh"
 
 namespace vy {
@@ -305,14 +307,15 @@ cudaError_t launch_linear_attn_chunked(const RecDev& d, int n_seqs, cudaStream_t
 
 // ---- tiled windowed attention --------------------------------------------------------------------------------------------
 constexpr int WT_M = 64;            // queries per CTA
-constexpr int WT_N = 64;            // keys per tile
-constexpr int WT_T = 256;           // threads: 16 x 16, each 4 query rows (ti + 16 r) by 4 key columns (tj + 16 c)
-constexpr int WT_LDP = WT_N + 4;
+constexpr int WT_T = 256;           // threads: 16 x 16, each 4 query rows (ti + 16 r) by BN / 16 key columns (tj + 16 c)
+// BN: keys per tile. 64 halves the barriers per key; 32 lets two CTAs share an SM at 128-wide heads (the kernel is bound by
+// shared-memory and FMA latency with 8 warps, so a second CTA is what fills the issue slots)
 
-template <int MV>
-__global__ void __launch_bounds__(WT_T, 1) window_attn_tiled_kernel(WinDev d, int ldq_s, int ldv_s, int dim4, int vdim4, bool qvec, bool kvvec) {
+template <int MV, int BN>
+__global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kernel(WinDev d, int ldq_s, int ldv_s, int dim4, int vdim4, bool qvec, bool kvvec) {
   pdl_trigger();
   pdl_wait();
+  constexpr int WT_N = BN, WT_LDP = BN + 4, NCB = BN / 16;
   extern __shared__ __align__(16) float wt_smem[];
   float* Qs = wt_smem;                       // [WT_M][ldq_s]
   float* Ks = Qs + WT_M * ldq_s;             // [WT_N][ldq_s]
@@ -364,27 +367,27 @@ __global__ void __launch_bounds__(WT_T, 1) window_attn_tiled_kernel(WinDev d, in
     rows_to_smem<WT_T>(Vs, ldv_s, WT_N, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE,
                  [&](int j) { return kpos_s[j] >= 0 ? static_cast<long long>(krow_s[j]) * vstride + static_cast<long long>(g) * d.vdim : -1LL; });
     __syncthreads();
-    float sc[4][4];
+    float sc[4][NCB];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) sc[r][c] = 0.f;
+      for (int c = 0; c < NCB; ++c) sc[r][c] = 0.f;
 #pragma unroll 2
     for (int d4 = 0; d4 < dim4; d4 += 4) {
-      float4 kv[4];
+      float4 kv[NCB];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) kv[c] = f4(Ks + (tj + 16 * c) * ldq_s + d4);
+      for (int c = 0; c < NCB; ++c) kv[c] = f4(Ks + (tj + 16 * c) * ldq_s + d4);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float4 qv = f4(Qs + (ti + 16 * r) * ldq_s + d4);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) sc[r][c] = dot4(qv, kv[c], sc[r][c]);
+        for (int c = 0; c < NCB; ++c) sc[r][c] = dot4(qv, kv[c], sc[r][c]);
       }
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < NCB; ++c) {
         const int i = ti + 16 * r, j = tj + 16 * c;
         const int p = p_lo + i, kp = kpos_s[j];
         const bool vis = i < rows && kp >= 0 && kp <= p && (d.window <= 0 || p - kp < d.window || kp < d.keep);
@@ -394,12 +397,12 @@ __global__ void __launch_bounds__(WT_T, 1) window_attn_tiled_kernel(WinDev d, in
 #pragma unroll
     for (int rr = 0; rr < 8; ++rr) {
       float* pr = Ps + (8 * warp + rr) * WT_LDP;
-      const float a = pr[lane], b = pr[lane + 32];
+      const float a = pr[lane], b = BN == 64 ? pr[lane + 32] : -INFINITY;
       const float mn = fmaxf(m[rr], warp_max(fmaxf(a, b)));
       const float cr = mn == -INFINITY ? 1.f : expf(m[rr] - mn);
       const float pa = a == -INFINITY ? 0.f : expf(a - mn), pb = b == -INFINITY ? 0.f : expf(b - mn);
       pr[lane] = pa;
-      pr[lane + 32] = pb;
+      if (BN == 64) pr[lane + 32] = pb;
       l[rr] = fmaf(l[rr], cr, warp_sum(pa + pb));
       m[rr] = mn;
       if (lane == 0) corr_s[8 * warp + rr] = cr;
@@ -457,8 +460,9 @@ __global__ void __launch_bounds__(WT_T, 1) window_attn_tiled_kernel(WinDev d, in
   }
 }
 
-template <int MV>
+template <int MV, int BN>
 static cudaError_t launch_wt(const WinDev& d, int n_seqs, int max_new, cudaStream_t st) {
+  constexpr int WT_N = BN, WT_LDP = BN + 4;
   const int dim4 = (d.dim + 3) & ~3, vdim4 = (d.vdim + 3) & ~3;
   const int ldq_s = ((dim4 >> 2) & 1) ? dim4 + 8 : dim4 + 4;   // (row stride / 4) odd: rows 1 apart start in distinct 16-byte bank groups
   const int ldv_s = vdim4 + 4;
@@ -469,18 +473,20 @@ static cudaError_t launch_wt(const WinDev& d, int n_seqs, int max_new, cudaStrea
   const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.kp) && al(d.vp);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(window_attn_tiled_kernel<MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(window_attn_tiled_kernel<MV, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     allowed = smem;
   }
-  return launch_kernel(window_attn_tiled_kernel<MV>, dim3((max_new + WT_M - 1) / WT_M, d.heads, n_seqs), dim3(WT_T), smem, st, d, ldq_s, ldv_s,
+  return launch_kernel(window_attn_tiled_kernel<MV, BN>, dim3((max_new + WT_M - 1) / WT_M, d.heads, n_seqs), dim3(WT_T), smem, st, d, ldq_s, ldv_s,
                        dim4, vdim4, qvec, kvvec);
 }
 
 cudaError_t launch_window_attn_tiled(const WinDev& d, int n_seqs, int max_new, cudaStream_t st) {
-  if (d.vdim <= 64) return launch_wt<1>(d, n_seqs, max_new, st);
-  if (d.vdim <= 128) return launch_wt<2>(d, n_seqs, max_new, st);
-  return launch_wt<4>(d, n_seqs, max_new, st);   // vdim <= 256 (checked by the caller)
+  static const int bn_env = getenv("VY_WINDOW_ATTN_BN") ? atoi(getenv("VY_WINDOW_ATTN_BN")) : 0;   // development: 32 or 64
+  const bool narrow = bn_env ? bn_env == 32 : (d.dim > 64 || d.vdim > 64);   // wide heads: 64-key tiles would take the SM for one CTA
+  if (d.vdim <= 64) return narrow ? launch_wt<1, 32>(d, n_seqs, max_new, st) : launch_wt<1, 64>(d, n_seqs, max_new, st);
+  if (d.vdim <= 128) return narrow ? launch_wt<2, 32>(d, n_seqs, max_new, st) : launch_wt<2, 64>(d, n_seqs, max_new, st);
+  return launch_wt<4, 64>(d, n_seqs, max_new, st);   // vdim <= 256 (checked by the caller): the accumulators leave no room for two CTAs
 }
 
 }  // namespace vy
