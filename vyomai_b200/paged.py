@@ -20,6 +20,8 @@ from __future__ import annotations
 
 import itertools
 from collections import deque
+
+import numpy as np
 from typing import Dict, Iterable, List
 
 import torch
@@ -209,6 +211,12 @@ class HybridSequence:
         self.num_cached = 0
         self.blocks: List[int] = []
         self.slot = -1
+        self._blocks_np = None   # `blocks` as an int32 array, rebuilt when the list changed (single-token steps copy it every step)
+
+    def blocks_array(self):
+        if self._blocks_np is None or len(self._blocks_np) != len(self.blocks):
+            self._blocks_np = np.asarray(self.blocks, dtype=np.int32)
+        return self._blocks_np
 
 
 class HybridCacheManager:
@@ -284,10 +292,12 @@ class HybridCacheManager:
             self._grow_blocks(max(need - len(self.free_blocks), self.num_blocks // 2, 1))
         for _ in range(max(need, 0)):
             seq.blocks.append(self.free_blocks.popleft())
+            seq._blocks_np = None
 
     def free(self, seq: HybridSequence) -> None:
         self.free_blocks.extend(seq.blocks)
         seq.blocks = []
+        seq._blocks_np = None
         if seq.slot >= 0:
             self.free_slots.append(seq.slot)
             seq.slot = -1
@@ -307,6 +317,7 @@ class _CapturedStep:
         _, total = engine._layout(n, width, n, n)
         self.flat = torch.zeros(total, dtype=torch.int32, device=engine.device)
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()   # the same pinned memory, filled in place by the engine
         self.copied = None
         batch, ids_t, rows_t = engine._views(self.flat, n, width, n, n, 1)
         self.graph = torch.cuda.CUDAGraph()
@@ -319,15 +330,22 @@ class _CapturedStep:
             if pdl:
                 _lib.lib().vy_set_pdl(prev)
 
-    def replay(self, host_ints: torch.Tensor) -> torch.Tensor:
+    def begin(self):
+        """The pinned staging array, free to be overwritten (the previous replay's upload has left it)."""
         if self.copied is not None:
-            self.copied.synchronize()   # the previous replay's upload has left the pinned buffer
-        self.host.copy_(host_ints)
+            self.copied.synchronize()
+        return self.host_np
+
+    def launch(self) -> torch.Tensor:
         self.flat.copy_(self.host, non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()
         self.graph.replay()
         return self.logits
+
+    def replay(self, host_ints: torch.Tensor) -> torch.Tensor:
+        self.begin()[:] = host_ints.numpy()
+        return self.launch()
 
 
 class HybridBatchEngine:
@@ -394,11 +412,7 @@ class HybridBatchEngine:
         single = max_new == 1 and self.use_graph
         if single:   # few distinct table widths, so few captures
             width = max(8, 1 << (width - 1).bit_length())
-        table = []
-        for seq, _ in work:
-            table += seq.blocks + [0] * (width - len(seq.blocks))
         if single:
-            host = torch.tensor(cu + pos0 + slot + table + ids + list(range(n)), dtype=torch.int32)
             key = (n, width, mgr.generation)
             if self._graphs and next(iter(self._graphs))[2] != mgr.generation:
                 self._graphs.clear()   # the pools were re-allocated: those captures point at freed tensors
@@ -408,15 +422,37 @@ class HybridBatchEngine:
                     self._graphs.clear()
                 cap = self._graphs[key] = _CapturedStep(self, n, width)
             self._seen[key] = self._seen.get(key, 0) + 1
+            # the step's integers go straight into the (pinned) staging array: no Python list of the block table per step
+            offs, total = self._layout(n, width, n, n)
+            buf = cap.begin() if cap is not None else np.empty(total, dtype=np.int32)
+            (o_cu, _), (o_pos, _), (o_slot, _), (o_tab, _), (o_ids, _), (o_rows, _) = offs
+            buf[o_cu:o_cu + n + 1] = np.arange(n + 1, dtype=np.int32)
+            buf[o_pos:o_pos + n] = pos0
+            buf[o_slot:o_slot + n] = slot
+            tab = buf[o_tab:o_tab + n * width].reshape(n, width)
+            tab[:] = 0
+            for i, (seq, _) in enumerate(work):
+                b = seq.blocks_array()
+                tab[i, :len(b)] = b
+            buf[o_ids:o_ids + n] = ids
+            buf[o_rows:o_rows + n] = np.arange(n, dtype=np.int32)
             if cap is not None:
-                all_rows = cap.replay(host)
-                logits = all_rows[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else None
+                all_rows = cap.launch()
             else:
-                flat = host.pin_memory().to(self.device, non_blocking=True)
+                flat = torch.from_numpy(buf)
+                flat = flat.pin_memory().to(self.device, non_blocking=True)
                 batch, ids_t, rows_t = self._views(flat, n, width, n, n, 1)
                 all_rows = self.model.step(ids_t, batch, mgr.views, rows_t)
-                logits = all_rows[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else None
+            if not rows:
+                logits = None
+            elif rows == list(range(n)):
+                logits = all_rows.clone() if cap is not None else all_rows   # every row wanted, in order (a replay's output buffer is reused)
+            else:
+                logits = all_rows[torch.tensor(rows, dtype=torch.long, device=self.device)]
         else:
+            table = []
+            for seq, _ in work:
+                table += seq.blocks + [0] * (width - len(seq.blocks))
             flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32)
             if self.device.type == "cuda":   # one pinned staging buffer, one host-to-device copy per step
                 flat = flat.pin_memory().to(self.device, non_blocking=True)
