@@ -288,6 +288,9 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
 constexpr int WD_WARPS = 8;
 constexpr int WD_KEYS = 4;
 
+// VEC: fp32 pages and query, dim and vdim multiples of 4, 16-byte aligned rows: lane l holds channels 4 l .. 4 l + 3 (+ 128) and
+// reads a key or value row with one 16-byte load per 128 channels instead of four 4-byte ones
+template <bool VEC>
 __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDev d) {
   pdl_trigger();
   pdl_wait();
@@ -298,10 +301,12 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
   if (d.cu[s + 1] - base <= 0) return;
   const int g = h / (d.heads / d.kv_heads);
   const long long qrow = base;
+  // channel of register slot r: strided by 32 (scalar form) or groups of 4 strided by 128 (vector form)
+  auto chan = [&](int r) { return VEC ? 4 * lane + 128 * (r >> 2) + (r & 3) : lane + 32 * r; };
   float qreg[WA_VR];
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
-    const int col = lane + 32 * r;
+    const int col = chan(r);
     qreg[r] = col < d.dim ? ld_as_float(d.q, d.q_dt, qrow * d.ldq + static_cast<long long>(h) * d.dim + col) * d.scale : 0.f;
   }
   const int pos = d.pos0[s];
@@ -328,21 +333,48 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
       row[u] = static_cast<long long>(tab[kp / d.bs]) * d.bs + kp % d.bs;
       sc[u] = 0.f;
     }
+    if constexpr (VEC) {
+      const float* kb = reinterpret_cast<const float*>(d.kp) + static_cast<long long>(g) * d.dim + 4 * lane;
+      const float* vb = reinterpret_cast<const float*>(d.vp) + static_cast<long long>(g) * d.vdim + 4 * lane;
 #pragma unroll
-    for (int r = 0; r < WA_VR; ++r) {
-      const int col = lane + 32 * r;
-      if (col < d.dim) {
+      for (int r4 = 0; r4 < WA_VR / 4; ++r4) {
+        if (4 * lane + 128 * r4 < d.dim) {
+#pragma unroll
+          for (int u = 0; u < WD_KEYS; ++u) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kb + row[u] * kstride + 128 * r4);
+            sc[u] = fmaf(qreg[4 * r4], k4.x, sc[u]);
+            sc[u] = fmaf(qreg[4 * r4 + 1], k4.y, sc[u]);
+            sc[u] = fmaf(qreg[4 * r4 + 2], k4.z, sc[u]);
+            sc[u] = fmaf(qreg[4 * r4 + 3], k4.w, sc[u]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r4 = 0; r4 < WA_VR / 4; ++r4) {
+#pragma unroll
+        for (int u = 0; u < WD_KEYS; ++u) {
+          float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (4 * lane + 128 * r4 < d.vdim) v4 = *reinterpret_cast<const float4*>(vb + row[u] * vstride + 128 * r4);
+          vv[u][4 * r4] = v4.x; vv[u][4 * r4 + 1] = v4.y; vv[u][4 * r4 + 2] = v4.z; vv[u][4 * r4 + 3] = v4.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < WA_VR; ++r) {
+        const int col = lane + 32 * r;
+        if (col < d.dim) {
+#pragma unroll
+          for (int u = 0; u < WD_KEYS; ++u)
+            sc[u] = fmaf(qreg[r], ld_as_float(d.kp, d.pool_dt, row[u] * kstride + static_cast<long long>(g) * d.dim + col), sc[u]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < WA_VR; ++r) {
+        const int col = lane + 32 * r;
 #pragma unroll
         for (int u = 0; u < WD_KEYS; ++u)
-          sc[u] = fmaf(qreg[r], ld_as_float(d.kp, d.pool_dt, row[u] * kstride + static_cast<long long>(g) * d.dim + col), sc[u]);
+          vv[u][r] = col < d.vdim ? ld_as_float(d.vp, d.pool_dt, row[u] * vstride + static_cast<long long>(g) * d.vdim + col) : 0.f;
       }
-    }
-#pragma unroll
-    for (int r = 0; r < WA_VR; ++r) {
-      const int col = lane + 32 * r;
-#pragma unroll
-      for (int u = 0; u < WD_KEYS; ++u)
-        vv[u][r] = col < d.vdim ? ld_as_float(d.vp, d.pool_dt, row[u] * vstride + static_cast<long long>(g) * d.vdim + col) : 0.f;
     }
     float m_new = m;
 #pragma unroll
@@ -373,7 +405,7 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
   if (lane == 0) { ms[warp] = m; ls[warp] = l; }
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
-    const int col = lane + 32 * r;
+    const int col = chan(r);
     if (col < d.vdim) as[warp * d.vdim + col] = acc[r];
   }
   __syncthreads();
@@ -391,7 +423,7 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
-    const int col = lane + 32 * r;
+    const int col = chan(r);
     if (col < d.vdim) {
       float a = 0.f;
 #pragma unroll
@@ -808,7 +840,10 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
     VY_CUDA_OK(launch_window_attn_tiled(d, p->n_seqs, p->max_new, st));
   } else if (p->max_new == 1) {
     const size_t smem = sizeof(float) * (2 * WD_WARPS + static_cast<size_t>(WD_WARPS) * p->vdim);
-    VY_CUDA_OK(launch_kernel(window_attn_decode_kernel, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d));
+    const auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+    const bool vec = p->pool_dtype == VY_F32 && p->dim % 4 == 0 && p->vdim % 4 == 0 && al(p->k_pool) && al(p->v_pool);
+    VY_CUDA_OK(vec ? launch_kernel(window_attn_decode_kernel<true>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d)
+                   : launch_kernel(window_attn_decode_kernel<false>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d));
   } else {
     const size_t smem = sizeof(float) * static_cast<size_t>(WA_WARPS) * p->dim;
     VY_CUDA_OK(launch_kernel(window_attn_kernel, dim3((p->max_new + WA_WARPS - 1) / WA_WARPS, p->heads, p->n_seqs), dim3(WA_WARPS * 32), smem,
