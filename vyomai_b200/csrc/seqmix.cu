@@ -442,9 +442,25 @@ struct ConvDev {
   float* state;
   int act;
   void* out; long long ld_out; int out_dt;
+  int fuse_state;   // every sequence's tokens fit one CTA row: the thread that read a channel's taps also writes the new ones
 };
 constexpr int CONV_MAX_TAPS = 16;
 constexpr int CONV_TOK = 32;
+
+// the last taps - 1 inputs of channel c after the step's n tokens (older ones come from the taps the slot held)
+__device__ __forceinline__ void conv_new_taps(const ConvDev& d, int c, int base, int n, bool carried, float* stp) {
+  float tmp[CONV_MAX_TAPS];
+#pragma unroll
+  for (int t = 0; t < CONV_MAX_TAPS - 1; ++t) {
+    if (t < d.taps - 1) {
+      const int j = n - (d.taps - 1) + t;
+      tmp[t] = j >= 0 ? ld_as_float(d.x, d.x_dt, static_cast<long long>(base + j) * d.ldx + c) : (carried ? stp[d.taps - 1 + j] : 0.f);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < CONV_MAX_TAPS - 1; ++t)
+    if (t < d.taps - 1) stp[t] = tmp[t];
+}
 
 __global__ void __launch_bounds__(128) causal_conv_kernel(ConvDev d) {
   pdl_trigger();
@@ -472,6 +488,8 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(ConvDev d) {
     }
     st_from_float(d.out, d.out_dt, static_cast<long long>(base + i) * d.ld_out + c, apply_uact(y, d.act));
   }
+  if (d.fuse_state && d.taps > 1 && n > 0)
+    conv_new_taps(d, c, base, n, carried, d.state + (static_cast<long long>(d.slot[s]) * d.channels + c) * (d.taps - 1));
 }
 
 __global__ void __launch_bounds__(128) causal_conv_state_kernel(ConvDev d) {
@@ -481,19 +499,7 @@ __global__ void __launch_bounds__(128) causal_conv_state_kernel(ConvDev d) {
   const int s = blockIdx.y;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
   if (c >= d.channels || n <= 0) return;
-  const bool carried = d.pos0[s] > 0;
-  float* stp = d.state + (static_cast<long long>(d.slot[s]) * d.channels + c) * (d.taps - 1);
-  float tmp[CONV_MAX_TAPS];
-#pragma unroll
-  for (int t = 0; t < CONV_MAX_TAPS - 1; ++t) {
-    if (t < d.taps - 1) {
-      const int j = n - (d.taps - 1) + t;
-      tmp[t] = j >= 0 ? ld_as_float(d.x, d.x_dt, static_cast<long long>(base + j) * d.ldx + c) : (carried ? stp[d.taps - 1 + j] : 0.f);
-    }
-  }
-#pragma unroll
-  for (int t = 0; t < CONV_MAX_TAPS - 1; ++t)
-    if (t < d.taps - 1) stp[t] = tmp[t];
+  conv_new_taps(d, c, base, n, d.pos0[s] > 0, d.state + (static_cast<long long>(d.slot[s]) * d.channels + c) * (d.taps - 1));
 }
 
 // ---- recurrences: one thread owns one column of the dim x vdim state in registers ---------------------------------------
@@ -870,13 +876,14 @@ extern "C" int vy_causal_conv(const VyCausalConv* p) {
   d.x = p->x; d.ldx = p->ldx; d.x_dt = p->x_dtype;
   d.w = p->w; d.w_dt = p->w_dtype;
   d.state = p->state; d.act = p->act;
+  d.fuse_state = p->max_new <= CONV_TOK ? 1 : 0;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   const int cb = (p->channels + 127) / 128;
   VY_CUDA_OK(launch_kernel(causal_conv_kernel, dim3(cb, (p->max_new + CONV_TOK - 1) / CONV_TOK, p->n_seqs), dim3(128), 0, st, d));
   VY_LAUNCH_OK();
   count_launch();
-  if (p->taps > 1) {
+  if (p->taps > 1 && !d.fuse_state) {
     VY_CUDA_OK(launch_kernel(causal_conv_state_kernel, dim3(cb, p->n_seqs), dim3(128), 0, st, d));
     VY_LAUNCH_OK();
     count_launch();
