@@ -118,8 +118,8 @@ __device__ __forceinline__ void axpyv(float (&acc)[NV], const float a, const flo
   for (int e = 0; e < NV; ++e) acc[e] = fmaf(a, x[e], acc[e]);
 }
 
-template <int DP, int VS>
-__global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kernel(RecDev d, bool vec) {
+template <int DP, int VS, int OCC>   // OCC: CTAs per SM the register budget is set for
+__global__ void __launch_bounds__(LA_T, OCC) linear_attn_chunk_kernel(RecDev d, bool vec) {
   pdl_trigger();
   pdl_wait();
   constexpr int LDQ = LaSmem<DP, VS>::LDQ, LDV = LaSmem<DP, VS>::LDV, LDP = LA_LDP;
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kern
 #pragma unroll
       for (int c = 0; c < 4; ++c) p[r][c] = 0.f;
     }
-#pragma unroll 2
+#pragma unroll (OCC == 1 ? 4 : 2)
     for (int d4 = 0; d4 < DP; d4 += 4) {
       float s0[NV], s1[NV], s2[NV], s3[NV];
       ldv<NV>(Ss + (d4 + 0) * LDV + NV * tj, s0);
@@ -277,25 +277,28 @@ __global__ void __launch_bounds__(LA_T, VS == 32 ? 2 : 1) linear_attn_chunk_kern
   }
 }
 
-template <int DP, int VS>
+template <int DP, int VS, int OCC>
 static cudaError_t launch_la(const RecDev& d, int n_seqs, cudaStream_t st) {
   constexpr size_t smem = sizeof(float) * LaSmem<DP, VS>::floats;
   static bool once = false;
   if (!once) {
-    cudaError_t e = cudaFuncSetAttribute(linear_attn_chunk_kernel<DP, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(linear_attn_chunk_kernel<DP, VS, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     once = true;
   }
   const auto al = [](const void* p, long long ld) { return reinterpret_cast<uintptr_t>(p) % 16 == 0 && ld % 4 == 0; };
   const bool vec = d.in_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.q, d.ldq) && al(d.k, d.ldk) && al(d.v, d.ldv);
-  return launch_kernel(linear_attn_chunk_kernel<DP, VS>, dim3((d.vdim + VS - 1) / VS, d.heads, n_seqs), dim3(LA_T), smem, st, d, vec);
+  return launch_kernel(linear_attn_chunk_kernel<DP, VS, OCC>, dim3((d.vdim + VS - 1) / VS, d.heads, n_seqs), dim3(LA_T), smem, st, d, vec);
 }
 
 template <int DP>
 static cudaError_t launch_la_dp(const RecDev& d, int n_seqs, cudaStream_t st) {
   // 64-column slices repeat the chunk's q k^T half as often; 32-column slices when those would leave SMs without a CTA
   const long long ctas64 = static_cast<long long>((d.vdim + 63) / 64) * d.heads * n_seqs;
-  return ctas64 >= 148 ? launch_la<DP, 64>(d, n_seqs, st) : launch_la<DP, 32>(d, n_seqs, st);
+  if (ctas64 >= 148) return launch_la<DP, 64, 1>(d, n_seqs, st);
+  const long long ctas32 = static_cast<long long>((d.vdim + 31) / 32) * d.heads * n_seqs;
+  // a grid that leaves every CTA an SM of its own gets the whole register file (deeper load / FMA overlap); otherwise two per SM
+  return ctas32 <= 148 ? launch_la<DP, 32, 1>(d, n_seqs, st) : launch_la<DP, 32, 2>(d, n_seqs, st);
 }
 
 cudaError_t launch_linear_attn_chunked(const RecDev& d, int n_seqs, cudaStream_t st) {
