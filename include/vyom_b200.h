@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define VY_ABI_VERSION 8
+#define VY_ABI_VERSION 9
 
 #if defined(__GNUC__)
 #define VY_API __attribute__((visibility("default")))
@@ -629,7 +629,7 @@ VY_API int vy_embed_bwd(const VyEmbed* p);
  * A step may mix sequences that start, continue with several tokens, or advance by one token.
  * Statistics, scores, softmax, decays and recurrent state are fp32 whatever the I/O dtypes.
  * ------------------------------------------------------------------------------------------ */
-enum { VY_UACT_NONE = 0, VY_UACT_RELU2 = 1, VY_UACT_SILU = 2, VY_UACT_SIGMOID = 3 };
+enum { VY_UACT_NONE = 0, VY_UACT_RELU2 = 1, VY_UACT_SILU = 2, VY_UACT_SIGMOID = 3, VY_UACT_GELU_TANH = 4 };
 
 /* out = act(A W^T + bias) * scale + addend, any M, N, K, any alignment; fp32 FMA accumulation (true fp32: no tf32). A and
  * W may have different dtypes (fp32 activations against bf16 weights). addend may alias out. scale 0 = 1. */
@@ -642,6 +642,9 @@ typedef struct VyLinear {
   int32_t act;
   float scale;
   void* out; int64_t ld_out; int32_t out_dtype;
+  /* batch > 1: `batch` independent products in one launch (one per attention head, say); product b reads A + b * a_batch,
+   * W + b * w_batch and writes out + b * out_batch (strides in elements; bias and addend must be null). 0 = 1. */
+  int32_t batch; int64_t a_batch, w_batch, out_batch;
   void* stream;
 } VyLinear;
 VY_API int vy_linear_plain(const VyLinear* p);
@@ -707,6 +710,9 @@ typedef struct VyWinAttn {
   const void* sink; int32_t sink_dtype;
   const void* gate; int64_t ld_gate; int32_t gate_dtype;
   void* out; int64_t ld_out; int32_t out_dtype;
+  /* row strides of the two pools in elements; 0 = kv_heads * dim and kv_heads * vdim. With explicit strides k_pool and v_pool
+   * may be views of ONE pool (latent attention: the value is the leading part of the key row). */
+  int64_t k_row, v_row;
   void* stream;
 } VyWinAttn;
 VY_API int vy_window_attn(const VyWinAttn* p);
@@ -769,6 +775,100 @@ typedef struct VyDeltaRule {
 VY_API int64_t vy_delta_rule_workspace_floats(int64_t rows, int32_t heads, int32_t kv_heads, int32_t dim);
 VY_API int vy_delta_rule(const VyDeltaRule* p);
 
+
+/* ---- latent attention and mixture-of-experts pieces (csrc/latent.cu) ---------------------------------------------------
+ * Pair rotation used below: of a vector's first `rot_dims` entries, (2i, 2i + 1) at position p become
+ * (u cos a - v sin a, v cos a + u sin a) with a = p * inv_freq[i] (fp32 table [rot_dims / 2], fp32 angle); the rest pass. */
+
+/* Writes the step's latent rows into a paged pool [num_blocks, block_size, pool_row]: x row = [rank latent | rot_dim key part];
+ * the latent is RMS-normed (plain weight [rank], eps inside the root), the key part rotated by the token's position, and
+ * [latent | key part] stored at the row of that position (same addressing as vy_kv_page_write). */
+typedef struct VyLatentWrite {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const int32_t* block_table; int32_t table_width, block_size;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  int32_t rank, rot_dim, rot_dims;
+  const float* inv_freq;
+  const void* weight; int32_t w_dtype;
+  float eps;
+  void* pool; int64_t pool_row; int32_t pool_dtype;
+  void* stream;
+} VyLatentWrite;
+VY_API int vy_latent_kv_write(const VyLatentWrite* p);
+
+/* Splits every head of a packed projection x[row, h * (pass + rot_dim) + ..] into its leading `pass` entries, copied to
+ * pass_out[row * ld_pass + h * pass + ..] (null = skipped), and its trailing rot_dim entries, rotated by the row's position
+ * and stored at rot_out[row * ld_rot + h * rot_head + rot_col + ..]. */
+typedef struct VyRopeSplit {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  int32_t heads, pass, rot_dim, rot_dims;
+  const float* inv_freq;
+  void* pass_out; int64_t ld_pass; int32_t pass_dtype;
+  void* rot_out; int64_t ld_rot; int32_t rot_head, rot_col; int32_t rot_dtype;
+  void* stream;
+} VyRopeSplit;
+VY_API int vy_rope_split(const VyRopeSplit* p);
+
+/* Router of a mixture of experts: score = sigmoid(logits[row, e]) (fp32 logits), the `top` largest (ties: lowest index),
+ * weight = score / (sum of the chosen scores + 1e-20) * scale. Writes idx [rows, top] int32 and weight [rows, top] fp32
+ * (largest first) and, when `dense` is given, dense[row, e] = weight or 0 ([rows, experts] fp32). experts <= 1024. */
+typedef struct VyMoeRoute {
+  int64_t rows; int32_t experts, top;
+  const float* logits; int64_t ld_logits;
+  float scale;
+  int32_t* idx; float* weight;
+  float* dense;
+  void* stream;
+} VyMoeRoute;
+VY_API int vy_moe_route(const VyMoeRoute* p);
+
+/* Weights the hidden activations of all experts at once: h [rows, experts * ff + shared_ff];
+ * out[row, e * ff + j] = h[..] * dense[row, e]; out[row, experts * ff + j] = h[..] * sigmoid(shared_gate[row * ld_gate])
+ * (shared_gate null = 1). A down projection over the whole row is then the weighted sum of the experts' outputs. experts may be 0
+ * (only the gated shared columns; dense unused). */
+typedef struct VyMoeScale {
+  int64_t rows; int32_t experts, ff, shared_ff;
+  const void* h; int64_t ldh; int32_t h_dtype;
+  const float* dense;
+  const float* shared_gate; int64_t ld_gate;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyMoeScale;
+VY_API int vy_moe_scale(const VyMoeScale* p);
+
+/* Sorted form for prompt-sized steps: each expert multiplies only the rows routed to it.
+ * vy_moe_sort: counts[e] = (row, k) pairs routed to expert e, offsets = their exclusive prefix sum ([experts + 1]),
+ * perm [rows * top] = the pair numbers row * top + k grouped by expert (in row order within an expert) and inv = the inverse
+ * of perm. vy_moe_gather: out[i, :] = x[perm[i] / top, :]. vy_moe_combine: out[row, :] = addend[row, :] + sum_k weight[row, k] *
+ * part[inv[row * top + k], :], summed in the order k = 0 .. top - 1 (no atomics: the result does not depend on the batch). */
+typedef struct VyMoeSort {
+  int64_t rows; int32_t experts, top;
+  const int32_t* idx;
+  int32_t* counts; int32_t* offsets; /* [experts], [experts + 1] */
+  int32_t* perm; int32_t* inv;       /* [rows * top] each */
+  void* stream;
+} VyMoeSort;
+VY_API int vy_moe_sort(const VyMoeSort* p);
+typedef struct VyMoeGather {
+  int64_t n; int32_t top, width;
+  const int32_t* perm;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyMoeGather;
+VY_API int vy_moe_gather(const VyMoeGather* p);
+typedef struct VyMoeCombine {
+  int64_t rows; int32_t top, width;
+  const int32_t* inv; const float* weight;
+  const void* part; int64_t ld_part; int32_t part_dtype;
+  const void* addend; int64_t ld_addend; int32_t addend_dtype; /* optional [rows, width] added (the shared expert) */
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyMoeCombine;
+VY_API int vy_moe_combine(const VyMoeCombine* p);
 
 /* vy_patchify — NCHW pixels -> [B * (H/ph) * (W/pw), C*ph*pw] patch rows, (c, i, j) order with j
  * fastest: the im2col of the stride==kernel nn.Conv2d at VyomAI/models/vision_encoder.py:83-88,114

@@ -17,4 +17,5 @@ from .generation_utils import generate, generate_multimodel, generate_seq2seq  #
 from .paged import ContinuousBatchEngine, PagedKVManager, SequenceState  # noqa: F401  (Examples/simple_vllm.ipynb)
 from .paged import HybridBatchEngine, HybridCacheManager, HybridSequence  # noqa: F401  (packed steps over pages + state slots)
 from .models.gelutar import GelutarConfig, GelutarForCausalLM  # noqa: F401
+from .models.zugunex import ZugunexConfig, ZugunexForCausalLM  # noqa: F401
 from .registry import load_model, register_model  # noqa: F401

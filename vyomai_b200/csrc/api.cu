@@ -205,6 +205,13 @@ int vy_abi_sizeof(const char* name) {
   VY_SZ(VyCausalConv);
   VY_SZ(VyLinAttn);
   VY_SZ(VyDeltaRule);
+  VY_SZ(VyLatentWrite);
+  VY_SZ(VyRopeSplit);
+  VY_SZ(VyMoeRoute);
+  VY_SZ(VyMoeScale);
+  VY_SZ(VyMoeSort);
+  VY_SZ(VyMoeGather);
+  VY_SZ(VyMoeCombine);
 #undef VY_SZ
   return -1;
 }

@@ -13,6 +13,7 @@ __device__ __forceinline__ float uact(float x, int act) {
     case VY_UACT_RELU2: { const float r = fmaxf(x, 0.f); return r * r; }
     case VY_UACT_SILU: return x / (1.f + expf(-x));
     case VY_UACT_SIGMOID: return 1.f / (1.f + expf(-x));
+    case VY_UACT_GELU_TANH: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
     default: return x;
   }
 }
@@ -25,7 +26,16 @@ struct LinDev {
   const void* addend; long long ld_addend; int addend_dt;
   int act; float scale;
   void* out; long long ld_out; int out_dt;
+  long long a_batch, w_batch, out_batch;   // element strides between the independent products of a batched call
 };
+
+// product b of a batched call: the same shapes at shifted base pointers
+__device__ __forceinline__ void lin_select(LinDev& d, int b) {
+  if (b == 0) return;
+  d.A = static_cast<const char*>(d.A) + d.a_batch * b * (d.a_dt == VY_F32 ? 4 : 2);
+  d.W = static_cast<const char*>(d.W) + d.w_batch * b * (d.w_dt == VY_F32 ? 4 : 2);
+  d.out = static_cast<char*>(d.out) + d.out_batch * b * (d.out_dt == VY_F32 ? 4 : 2);
+}
 
 __device__ __forceinline__ void lin_store(const LinDev& d, int m, int n, float acc) {
   if (d.bias) acc += ld_as_float(d.bias, d.bias_dt, n);
@@ -39,6 +49,7 @@ constexpr int LT = 64, LK = 16;
 __global__ void __launch_bounds__(256) linear_tile_kernel(LinDev d) {
   pdl_trigger();
   pdl_wait();
+  lin_select(d, blockIdx.z);
   __shared__ float As[LK][LT + 4];
   __shared__ float Ws[LK][LT + 4];
   const int m0 = blockIdx.y * LT, n0 = blockIdx.x * LT;
@@ -82,6 +93,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinDev d) {
 __global__ void __launch_bounds__(256) linear_rows_kernel(LinDev d) {
   pdl_trigger();
   pdl_wait();
+  lin_select(d, blockIdx.y);
   const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (n >= d.N) return;
@@ -142,7 +154,9 @@ extern "C" int vy_linear_plain(const VyLinear* p) {
   VY_CHECK_ARG(p->A && p->W && p->out, "vy_linear_plain: null operand");
   VY_CHECK_ARG(dtype_ok(p->a_dtype) && dtype_ok(p->w_dtype) && dtype_ok(p->out_dtype), "vy_linear_plain: bad dtype");
   VY_CHECK_ARG(p->lda >= p->K && p->ldw >= p->K && p->ld_out >= p->N, "vy_linear_plain: leading dimension smaller than the row");
-  VY_CHECK_ARG(p->act >= VY_UACT_NONE && p->act <= VY_UACT_SIGMOID, "vy_linear_plain: bad act %d", p->act);
+  VY_CHECK_ARG(p->act >= VY_UACT_NONE && p->act <= VY_UACT_GELU_TANH, "vy_linear_plain: bad act %d", p->act);
+  const int batch = p->batch > 1 ? p->batch : 1;
+  VY_CHECK_ARG(batch <= 65535 && (batch == 1 || (!p->bias && !p->addend)), "vy_linear_plain: a batched call takes no bias / addend (batch %d)", batch);
   if (p->bias) VY_CHECK_ARG(dtype_ok(p->bias_dtype), "vy_linear_plain: bad bias_dtype");
   if (p->addend) VY_CHECK_ARG(dtype_ok(p->addend_dtype) && p->ld_addend >= p->N, "vy_linear_plain: bad addend");
   LinDev d;
@@ -153,12 +167,13 @@ extern "C" int vy_linear_plain(const VyLinear* p) {
   d.addend = p->addend; d.ld_addend = p->ld_addend; d.addend_dt = p->addend_dtype;
   d.act = p->act; d.scale = p->scale == 0.f ? 1.f : p->scale;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
+  d.a_batch = p->a_batch; d.w_batch = p->w_batch; d.out_batch = p->out_batch;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   if (p->M <= 8) {
-    VY_CUDA_OK(launch_kernel(linear_rows_kernel, dim3((p->N + 7) / 8), dim3(256), 0, st, d));
+    VY_CUDA_OK(launch_kernel(linear_rows_kernel, dim3((p->N + 7) / 8, batch), dim3(256), 0, st, d));
   } else {
     VY_CHECK_ARG((p->M + LT - 1) / LT <= 65535, "vy_linear_plain: too many rows (%d)", p->M);
-    VY_CUDA_OK(launch_kernel(linear_tile_kernel, dim3((p->N + LT - 1) / LT, (p->M + LT - 1) / LT), dim3(256), 0, st, d));
+    VY_CUDA_OK(launch_kernel(linear_tile_kernel, dim3((p->N + LT - 1) / LT, (p->M + LT - 1) / LT, batch), dim3(256), 0, st, d));
   }
   VY_LAUNCH_OK();
   count_launch();
@@ -173,7 +188,7 @@ extern "C" int vy_unary(int64_t rows, int32_t cols, const void* x, int64_t ldx, 
     return VY_ERR_NO_DEVICE;
   }
   VY_CHECK_ARG(rows > 0 && cols > 0 && x && out, "vy_unary: bad arguments");
-  VY_CHECK_ARG(dtype_ok(x_dtype) && dtype_ok(out_dtype) && act >= VY_UACT_NONE && act <= VY_UACT_SIGMOID, "vy_unary: bad dtype / act");
+  VY_CHECK_ARG(dtype_ok(x_dtype) && dtype_ok(out_dtype) && act >= VY_UACT_NONE && act <= VY_UACT_GELU_TANH, "vy_unary: bad dtype / act");
   long long blocks = (rows * cols + 255) / 256;
   if (blocks > 16LL * num_sms()) blocks = 16LL * num_sms();
   VY_CUDA_OK(launch_kernel(unary_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),

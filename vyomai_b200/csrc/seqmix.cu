@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) acc[r] = 0.f;
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
-  const int kstride = d.kv_heads * d.dim, vstride = d.kv_heads * d.vdim;
+  const long long kstride = d.k_row, vstride = d.v_row;
   const int tiles = (count + 31) >> 5;
   for (int tt = 0; tt < tiles; ++tt) {
     const int c = tt * 32 + lane;
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) acc[r] = 0.f;
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
-  const long long kstride = static_cast<long long>(d.kv_heads) * d.dim, vstride = static_cast<long long>(d.kv_heads) * d.vdim;
+  const long long kstride = d.k_row, vstride = d.v_row;
   for (int c0 = WD_KEYS * warp; c0 < count; c0 += WD_KEYS * WD_WARPS) {
     long long row[WD_KEYS];
     float sc[WD_KEYS], vv[WD_KEYS][WA_VR];
@@ -835,6 +835,10 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
   d.cu = p->cu_tokens; d.pos0 = p->pos0; d.table = p->block_table; d.tw = p->table_width; d.bs = p->block_size;
   d.q = p->q; d.ldq = p->ldq; d.q_dt = p->q_dtype;
   d.kp = p->k_pool; d.vp = p->v_pool; d.pool_dt = p->pool_dtype;
+  d.k_row = p->k_row > 0 ? p->k_row : static_cast<long long>(p->kv_heads) * p->dim;
+  d.v_row = p->v_row > 0 ? p->v_row : static_cast<long long>(p->kv_heads) * p->vdim;
+  VY_CHECK_ARG(d.k_row >= static_cast<long long>(p->kv_heads) * p->dim && d.v_row >= static_cast<long long>(p->kv_heads) * p->vdim,
+               "vy_window_attn: pool row strides smaller than the rows");
   d.heads = p->heads; d.kv_heads = p->kv_heads; d.dim = p->dim; d.vdim = p->vdim;
   d.scale = p->scale; d.window = p->window; d.keep = p->keep_first;
   d.sink = p->sink; d.sink_dt = p->sink_dtype;
@@ -847,7 +851,7 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
   } else if (p->max_new == 1) {
     const size_t smem = sizeof(float) * (2 * WD_WARPS + static_cast<size_t>(WD_WARPS) * p->vdim);
     const auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
-    const bool vec = p->pool_dtype == VY_F32 && p->dim % 4 == 0 && p->vdim % 4 == 0 && al(p->k_pool) && al(p->v_pool);
+    const bool vec = p->pool_dtype == VY_F32 && p->dim % 4 == 0 && p->vdim % 4 == 0 && d.k_row % 4 == 0 && d.v_row % 4 == 0 && al(p->k_pool) && al(p->v_pool);
     VY_CUDA_OK(vec ? launch_kernel(window_attn_decode_kernel<true>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d)
                    : launch_kernel(window_attn_decode_kernel<false>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d));
   } else {

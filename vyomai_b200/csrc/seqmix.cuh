@@ -15,6 +15,7 @@ __device__ __forceinline__ float apply_uact(float x, int act) {
     case VY_UACT_RELU2: { const float r = fmaxf(x, 0.f); return r * r; }
     case VY_UACT_SILU: return siluf_(x);
     case VY_UACT_SIGMOID: return sigmoidf_(x);
+    case VY_UACT_GELU_TANH: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
     default: return x;
   }
 }
@@ -34,6 +35,7 @@ struct WinDev {
   const int* cu; const int* pos0; const int* table; int tw, bs;
   const void* q; long long ldq; int q_dt;
   const void* kp; const void* vp; int pool_dt;
+  long long k_row, v_row;   // row strides of the pools in elements (kv_heads * dim and kv_heads * vdim unless the caller views one pool twice)
   int heads, kv_heads, dim, vdim;
   float scale; int window, keep;
   const void* sink; int sink_dt;

@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kern
     for (int mm = 0; mm < MV; ++mm)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[r][mm][e] = 0.f;
-  const long long kstride = static_cast<long long>(d.kv_heads) * d.dim, vstride = static_cast<long long>(d.kv_heads) * d.vdim;
+  const long long kstride = d.k_row, vstride = d.v_row;
   for (int c0 = 0; c0 < count; c0 += WT_N) {
     __syncthreads();
     if (t < WT_N) {
@@ -473,7 +473,7 @@ static cudaError_t launch_wt(const WinDev& d, int n_seqs, int max_new, cudaStrea
                       sizeof(int) * 2 * WT_N;
   const auto al = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool qvec = d.q_dt == VY_F32 && d.dim % 4 == 0 && d.ldq % 4 == 0 && al(d.q);
-  const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.kp) && al(d.vp);
+  const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && d.k_row % 4 == 0 && d.v_row % 4 == 0 && al(d.kp) && al(d.vp);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
     cudaError_t e = cudaFuncSetAttribute(window_attn_tiled_kernel<MV, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

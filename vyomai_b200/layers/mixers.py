@@ -1,5 +1,5 @@
-"""Sequence mixers and the squared-ReLU feed-forward of the hybrid decoder family (models/gelutar.py), on the packed-batch
-kernels of csrc/seqmix.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
+"""Sequence mixers and feed-forwards of the packed-step decoder families (models/gelutar.py, models/zugunex.py), on the
+packed-batch kernels of csrc/seqmix.cu and csrc/latent.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
 (`cache_spec`: pages of keys / values, recurrent state slots) and maps the normed layer input h [rows, width] to its
 output; the constants of a mechanism (window, kept tokens, scale, sink, decay, taps, head counts) are constructor
 arguments, so another architecture can reuse a mixer with other values.
@@ -26,7 +26,9 @@ class Projection:
     tcgen05 / small-batch GEMM (vy_gemm, fp32 result); fp32 weights and every other shape go to the fp32-FMA kernel."""
 
     def __init__(self, weight: torch.Tensor, tensor_cores: bool = True):
-        self.weight = weight.contiguous()
+        # a column slice of a wider matrix (unit column stride, 16-byte aligned rows) is used in place, not copied
+        view_ok = weight.dim() == 2 and weight.stride(1) == 1 and (weight.stride(0) * weight.element_size()) % 16 == 0 and weight.data_ptr() % 16 == 0
+        self.weight = weight if view_ok else weight.contiguous()
         self.out_features, self.in_features = weight.shape
         self.tensor_cores = bool(tensor_cores) and weight.dtype == torch.bfloat16 and self.in_features % 8 == 0 and self.in_features >= 32 \
             and self.out_features >= 16
@@ -37,7 +39,7 @@ class Projection:
         if out is None:
             out = torch.empty((x.shape[0], _round_up(N, 8)), device=x.device, dtype=out_dtype)[:, :N]
         tc = self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and bias is None \
-            and act in (None, "none", "relu2")
+            and act in (None, "none", "relu2", "gelu_tanh")
         if tc:
             ops.gemm(x, self.weight, act=act, addend=addend, out=out, out_scale=scale, swap_ab=x.shape[0] <= 32)
         else:
@@ -183,13 +185,166 @@ class GatedDeltaMixer(Mixer):
         return self.o(on)
 
 
-class ReluSquaredMLP:
-    """W_down relu(W_up h)^2, the down projection adding into the fp32 residual in its epilogue."""
+class LatentAttention(Mixer):
+    """Attention whose keys and values are linear images of a cached low-rank latent: per token the cache holds the RMS-normed
+    latent c [rank] and one rotated key part kr [rot_dim] shared by the heads. Head h scores (qn_h . W_uk_h c + qr_h . kr) * scale
+    and outputs W_uv_h sum_j p_j c_j, so the kernels never expand keys or values: the unrotated query part is carried into latent
+    space once per token (qa_h = W_uk_h^T qn_h) and the attention runs with ONE key/value head over rows [c | kr] (key = the whole
+    row, value = its first `rank` entries, both views of one pool), followed by the per-head value expansion. Pair rotation by
+    position on the rotated parts, sliding window, softmax sink and sigmoid output gate as in WindowSinkAttention. A mixer built
+    with `shared_from` owns no down-projection: it reads the pool of the layer it names with its own W_uk / W_uv / queries."""
+
+    def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool,
+                 kv_dtype: torch.dtype = torch.float32, shared_from: Optional[int] = None):
+        self.heads, self.dim, self.rot_dim = int(cfg["heads"]), int(cfg["dim"]), int(cfg["rot_dim"])
+        self.vdim, self.rank = int(cfg["vdim"]), int(cfg["kv_rank"])
+        rot = cfg.get("rot") or {}
+        self.rot_dims = int(rot.get("dims", self.rot_dim)) if self.rot_dim else 0
+        if self.rot_dims > self.rot_dim or self.rot_dims % 2:
+            raise ValueError("latent attention: rot.dims must be even and at most rot_dim")
+        self.window = int((cfg.get("mask") or {}).get("size", 0))
+        self.scale = float(cfg["scale"])
+        self.eps, self.act_dtype, self.kv_dtype, self.shared_from = eps, act_dtype, kv_dtype, shared_from
+        self.tensor_cores = bool(tensor_cores) and w["q"].dtype == torch.bfloat16
+        dev = w["q"].device
+        base = float(rot.get("base", 10000.0))
+        f = [base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)] or [0.0]
+        self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(dev)
+        self.row = self.rank + self.rot_dim   # one pool row: [latent | rotated key part]
+        if self.row > 256 or self.rank > 256:
+            raise ValueError(f"latent attention: kv_rank + rot_dim = {self.row} exceeds the attention kernels' 256 channels per head")
+        H, dn, R, dv = self.heads, self.dim, self.rank, self.vdim
+        self._in = [w["q"]] + ([] if shared_from is not None else [w["dkv"]]) + [w["g"]]
+        self.dkv_norm = None if shared_from is not None else w["dkv.norm"].contiguous()
+        self.uk_t = w["uk"].view(H, dn, R).transpose(1, 2).contiguous()   # [H, R, dn]: head h maps qn_h to latent space
+        self.uv = w["uv"].view(H, dv, R).contiguous()                       # [H, dv, R]
+        self.sink = w["sink"].contiguous() if "sink" in w else None
+        self.o = Projection(w["o"], tensor_cores)
+
+    def input_weights(self):
+        return self._in
+
+    def cache_spec(self):
+        if self.shared_from is not None:
+            return {"pages": None, "states": {}, "pages_from": (self.shared_from, 0)}
+        return {"pages": (1, self.row, 0), "states": {}, "kv_dtype": self.kv_dtype}
+
+    def _per_head(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head: int, out_head: int) -> None:
+        """out[:, h * out_head : + N] = x[:, h * x_head : + K] @ w[h].T for every head: tensor-core products per head for prompt-sized
+        steps when the slices are aligned for them, one batched fp32-FMA launch otherwise."""
+        H, N, K = w.shape
+        es_o = out.element_size()
+        tc = self.tensor_cores and x.shape[0] > 32 and x.dtype == torch.bfloat16 and K % 8 == 0 and K >= 32 and N >= 16 and x_head % 8 == 0 \
+            and (out_head * es_o) % 16 == 0 and (out.stride(0) * es_o) % 16 == 0 and x.stride(0) % 8 == 0
+        if not tc:
+            ops.head_linear(x, w, out, x_head=x_head, out_head=out_head)
+            return
+        for h in range(H):
+            ops.gemm(x[:, h * x_head:h * x_head + K], w[h], out=out[:, h * out_head:h * out_head + N])
+
+    def forward(self, parts, batch, cache):
+        if self.shared_from is None:
+            q, dkv, g = parts
+            ops.latent_kv_write(batch, dkv, self.dkv_norm, self.inv_freq, cache.k_pool, rank=self.rank, rot_dim=self.rot_dim,
+                                rot_dims=self.rot_dims, eps=self.eps)
+        else:
+            q, g = parts
+        rows, H = q.shape[0], self.heads
+        Q = torch.empty((rows, H * self.row), device=q.device, dtype=torch.float32)
+        qn = torch.empty((rows, H * self.dim), device=q.device, dtype=self.act_dtype)
+        ops.rope_split(batch, q, self.inv_freq, heads=H, keep=self.dim, rot_dim=self.rot_dim, rot_dims=self.rot_dims, pass_out=qn, rot_out=Q,
+                       rot_head=self.row, rot_col=self.rank)
+        self._per_head(qn, self.uk_t, Q, self.dim, self.row)
+        pool = cache.k_pool
+        a = ops.window_attn(batch, Q, pool, pool, heads=H, kv_heads=1, dim=self.row, vdim=self.rank, scale=self.scale, window=self.window,
+                            keep_first=0, sink=self.sink, gate=g, out_dtype=self.act_dtype, k_row=self.row, v_row=self.row)
+        o = torch.empty((rows, H * self.vdim), device=q.device, dtype=self.act_dtype)
+        self._per_head(a, self.uv, o, self.rank, self.vdim)
+        return self.o(o)
+
+
+class DenseMLP:
+    """W_down act(W_up h). With `x_residual` the down projection adds into the fp32 residual in its epilogue; without, it
+    returns the fp32 result (models that norm a sublayer's OUTPUT)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], act_dtype: torch.dtype, tensor_cores: bool, act: str = "relu2"):
+        self.up, self.down = Projection(w["up"], tensor_cores), Projection(w["down"], tensor_cores)
+        self.act_dtype, self.act = act_dtype, act
+
+    def forward(self, h: torch.Tensor, x_residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        u = self.up(h, act=self.act, out_dtype=self.act_dtype)   # activation on the fp32 accumulator in the epilogue, rounded once
+        if x_residual is None:
+            return self.down(u)
+        return self.down(u, addend=x_residual, out=x_residual)
+
+
+class ReluSquaredMLP(DenseMLP):
+    """W_down relu(W_up h)^2."""
 
     def __init__(self, w: Dict[str, torch.Tensor], act_dtype: torch.dtype, tensor_cores: bool):
-        self.up, self.down = Projection(w["up"], tensor_cores), Projection(w["down"], tensor_cores)
-        self.act_dtype = act_dtype
+        super().__init__(w, act_dtype, tensor_cores, act="relu2")
 
-    def forward(self, h: torch.Tensor, x_residual: torch.Tensor) -> torch.Tensor:
-        u = self.up(h, act="relu2", out_dtype=self.act_dtype)   # squared on the fp32 accumulator in the epilogue, rounded once
-        return self.down(u, addend=x_residual, out=x_residual)
+
+class MoEFeedForward:
+    """Mixture of experts W_down_e act(W_up_e h) with a sigmoid router: the `top` largest scores are kept, divided by their sum
+    and multiplied by `route_scale`; an optional shared expert runs for every token, times sigmoid(w_sg . h). Router logits and
+    the shared gate are one fp32 product read from the fp32 layer input.
+
+    Two exact forms of the same sum. Single tokens and short steps (also every CUDA-graph-captured step: no host decision)
+    run ALL experts as two products over the concatenated experts, the hidden activations multiplied by each token's routing
+    weight (0 for the experts it did not choose) in between: the weights are read once, as a decode step would anyway.
+    Prompt-sized steps sort the (token, choice) pairs by expert on the device, gather the rows, run each expert's two products
+    on its own rows, and combine per token in choice order (no atomics, so the result does not depend on the batch)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], experts: int, top: int, route_scale: float, act_dtype: torch.dtype, tensor_cores: bool,
+                 act: str = "relu2", shared: bool = False, sorted_min_rows: int = 128):
+        self.experts, self.top, self.route_scale = int(experts), int(top), float(route_scale)
+        self.act_dtype, self.act, self.sorted_min_rows = act_dtype, act, int(sorted_min_rows)
+        E = self.experts
+        self.ff = w["e0.up"].shape[0]
+        ups = [w[f"e{e}.up"] for e in range(E)]
+        downs = [w[f"e{e}.down"] for e in range(E)]
+        self.shared_ff = 0
+        rt = [w["router"]]
+        if shared:
+            self.shared_ff = w["shared.up"].shape[0]
+            ups.append(w["shared.up"])
+            downs.append(w["shared.down"])
+            rt.append(w["shared.sg"].reshape(1, -1))
+        up_all = torch.cat(ups, 0).contiguous()        # [E ff + S, W]
+        down_all = torch.cat(downs, 1).contiguous()    # [W, E ff + S]
+        self.up_all, self.down_all = Projection(up_all, tensor_cores), Projection(down_all, tensor_cores)
+        self.router = torch.cat(rt, 0).contiguous()    # [E (+ 1), W]: fp32 FMA against the fp32 layer input
+        f = self.ff
+        self.up_e = [Projection(up_all[e * f:(e + 1) * f], tensor_cores) for e in range(E)]
+        self.down_e = [Projection(down_all[:, e * f:(e + 1) * f], tensor_cores) for e in range(E)]
+        if shared:
+            self.up_s = Projection(up_all[E * f:], tensor_cores)
+            self.down_s = Projection(down_all[:, E * f:], tensor_cores)
+
+    def forward(self, h: torch.Tensor, x32: torch.Tensor, batch) -> torch.Tensor:
+        """h: the layer input in the activation dtype, x32: the same rows in fp32 (router input). Returns fp32 [rows, width]."""
+        E, rows = self.experts, h.shape[0]
+        z = ops.linear_plain(x32, self.router, out_dtype=torch.float32)
+        sorted_form = batch.max_new > 1 and rows >= self.sorted_min_rows
+        idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form)
+        sg = z[:, E:E + 1] if self.shared_ff else None
+        if not sorted_form:
+            u = self.up_all(h, act=self.act, out_dtype=torch.float32)
+            us = ops.moe_scale(u, dense, experts=E, ff=self.ff, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype)
+            return self.down_all(us)
+        counts, offsets, perm, inv = ops.moe_sort(idx, E)
+        xg = ops.moe_gather(h, perm, self.top, self.act_dtype)
+        off = offsets.cpu().tolist()   # the one host decision of a prompt step: how many rows each expert got
+        part = torch.empty((rows * self.top, self.down_all.out_features), device=h.device, dtype=torch.float32)
+        for e in range(E):
+            a, b = off[e], off[e + 1]
+            if b > a:
+                u = self.up_e[e](xg[a:b], act=self.act, out_dtype=self.act_dtype)
+                self.down_e[e](u, out=part[a:b])
+        ys = None
+        if self.shared_ff:
+            u = self.up_s(h, act=self.act, out_dtype=torch.float32)
+            us = ops.moe_scale(u, None, experts=0, ff=1, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype)
+            ys = self.down_s(us)
+        return ops.moe_combine(part, inv, wt, addend=ys)

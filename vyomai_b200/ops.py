@@ -862,7 +862,7 @@ def adamw(param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_dec
 
 # ---- sequence-mixer family (csrc/seqmix.cu, csrc/linear_plain.cu): packed batches, fp32 statistics and state ----
 UACT = {None: C["VY_UACT_NONE"], "none": C["VY_UACT_NONE"], "relu2": C["VY_UACT_RELU2"], "silu": C["VY_UACT_SILU"],
-        "sigmoid": C["VY_UACT_SIGMOID"]}
+        "sigmoid": C["VY_UACT_SIGMOID"], "gelu_tanh": C["VY_UACT_GELU_TANH"]}
 W_MODE = {None: 0, "plain": 1, "one_plus": 2}
 
 
@@ -890,6 +890,21 @@ class PackedBatch:
 def _rows2d(t: torch.Tensor, what: str) -> None:
     if t.dim() != 2 or t.stride(1) != 1:
         raise _lib.VyomError(f"{what}: expected a 2-d tensor with unit column stride, got shape {tuple(t.shape)} strides {t.stride()}")
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, x_head: int, out_head: int) -> torch.Tensor:
+    """One launch of `heads` independent products with fp32 FMA accumulation: w is [heads, N, K]; head h reads x[:, h * x_head : h * x_head + K]
+    and writes out[:, h * out_head : h * out_head + N]."""
+    _need_cuda(x, w, out)
+    _rows2d(x, "head_linear x")
+    _rows2d(out, "head_linear out")
+    heads, N, K = w.shape
+    if not w.is_contiguous() or (heads - 1) * x_head + K > x.shape[1] or (heads - 1) * out_head + N > out.shape[1]:
+        raise _lib.VyomError("head_linear: weight layout / head strides do not fit the operands")
+    _lib.call("vy_linear_plain", "VyLinear", M=x.shape[0], N=N, K=K, A=x.data_ptr(), lda=x.stride(0), a_dtype=_dt(x), W=w.data_ptr(), ldw=K,
+              w_dtype=_dt(w), act=UACT[None], scale=1.0, out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), batch=heads, a_batch=x_head,
+              w_batch=N * K, out_batch=out_head, stream=_stream())
+    return out
 
 
 def linear_plain(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: Optional[str] = None, scale: float = 1.0,
@@ -976,10 +991,11 @@ def kv_page_write(batch: PackedBatch, k: torch.Tensor, v: torch.Tensor, k_pool: 
 
 def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
                 vdim: int, scale: float, window: int, keep_first: int, sink: Optional[torch.Tensor] = None,
-                gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, k_row: int = 0, v_row: int = 0) -> torch.Tensor:
     """Attention of the step's queries over the paged pools (which already hold the step's keys): causal, restricted to the last
     `window` positions plus the first `keep_first` ones, optional per-head sink in the softmax denominator, optional per-head
-    sigmoid output gate."""
+    sigmoid output gate. k_row / v_row: row strides of the pools in elements when they are not kv_heads * dim | vdim (two views of
+    one pool)."""
     _need_cuda(q, k_pool, v_pool, sink, gate)
     _rows2d(q, "window_attn q")
     out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or q.dtype)
@@ -987,7 +1003,101 @@ def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_poo
               v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale),
               window=int(window), keep_first=int(keep_first), sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
               gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0, gate_dtype=_dt(gate) if gate is not None else 0,
-              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw(pages=True, slots=False))
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), k_row=int(k_row), v_row=int(v_row), stream=_stream(),
+              **batch._kw(pages=True, slots=False))
+    return out
+
+
+def latent_kv_write(batch: PackedBatch, x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, pool: torch.Tensor, *, rank: int, rot_dim: int,
+                    rot_dims: int, eps: float) -> None:
+    """x [rows, rank + rot_dim] -> pool rows [RMS-normed latent * weight | key part rotated by position] at each token's page row."""
+    _need_cuda(x, weight, inv_freq, pool)
+    _rows2d(x, "latent_kv_write x")
+    if not pool.is_contiguous() or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2 or weight.numel() != rank:
+        raise _lib.VyomError("latent_kv_write: pool contiguous, inv_freq fp32 [rot_dims / 2], weight [rank]")
+    _lib.call("vy_latent_kv_write", "VyLatentWrite", x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), rank=rank, rot_dim=rot_dim, rot_dims=rot_dims,
+              inv_freq=inv_freq.data_ptr(), weight=weight.data_ptr(), w_dtype=_dt(weight), eps=float(eps), pool=pool.data_ptr(),
+              pool_row=pool.shape[-1] * pool.shape[-2] if pool.dim() == 4 else pool.shape[-1], pool_dtype=_dt(pool), stream=_stream(),
+              **batch._kw(pages=True, slots=False))
+
+
+def rope_split(batch: PackedBatch, x: torch.Tensor, inv_freq: torch.Tensor, *, heads: int, keep: int, rot_dim: int, rot_dims: int,
+               pass_out: Optional[torch.Tensor], rot_out: torch.Tensor, rot_head: int, rot_col: int) -> None:
+    """Per head of x [rows, heads * (keep + rot_dim)]: the leading `keep` entries are copied to pass_out [rows, heads * keep], the
+    trailing rot_dim ones rotated by position into rot_out[:, h * rot_head + rot_col : .. + rot_dim]."""
+    _need_cuda(x, inv_freq, pass_out, rot_out)
+    _rows2d(x, "rope_split x")
+    _rows2d(rot_out, "rope_split rot_out")
+    if pass_out is not None:
+        _rows2d(pass_out, "rope_split pass_out")
+    _lib.call("vy_rope_split", "VyRopeSplit", x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), heads=heads, **{"pass": keep}, rot_dim=rot_dim,
+              rot_dims=rot_dims, inv_freq=inv_freq.data_ptr(), pass_out=_ptr(pass_out), ld_pass=pass_out.stride(0) if pass_out is not None else 0,
+              pass_dtype=_dt(pass_out) if pass_out is not None else 0, rot_out=rot_out.data_ptr(), ld_rot=rot_out.stride(0), rot_head=rot_head,
+              rot_col=rot_col, rot_dtype=_dt(rot_out), stream=_stream(), **batch._kw(slots=False))
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, dense: bool = True):
+    """fp32 logits [rows, >= experts] -> (idx [rows, top] int32, weight [rows, top] fp32, dense [rows, experts] fp32 or None)."""
+    _need_cuda(logits)
+    _rows2d(logits, "moe_route logits")
+    if logits.dtype != torch.float32:
+        raise _lib.VyomError("moe_route: logits are fp32")
+    rows = logits.shape[0]
+    idx = torch.empty((rows, top), device=logits.device, dtype=torch.int32)
+    wt = torch.empty((rows, top), device=logits.device, dtype=torch.float32)
+    dn = torch.empty((rows, experts), device=logits.device, dtype=torch.float32) if dense else None
+    _lib.call("vy_moe_route", "VyMoeRoute", rows=rows, experts=experts, top=top, logits=logits.data_ptr(), ld_logits=logits.stride(0),
+              scale=float(scale), idx=idx.data_ptr(), weight=wt.data_ptr(), dense=_ptr(dn), stream=_stream())
+    return idx, wt, dn
+
+
+def moe_scale(h: torch.Tensor, dense: Optional[torch.Tensor], *, experts: int, ff: int, shared_ff: int, shared_gate: Optional[torch.Tensor],
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """h [rows, experts * ff + shared_ff] times each column's routing weight (dense [rows, experts]; the shared columns times
+    sigmoid(shared_gate[row, 0]))."""
+    _need_cuda(h, dense, shared_gate)
+    _rows2d(h, "moe_scale h")
+    out = torch.empty(h.shape, device=h.device, dtype=out_dtype)
+    _lib.call("vy_moe_scale", "VyMoeScale", rows=h.shape[0], experts=experts, ff=ff, shared_ff=shared_ff, h=h.data_ptr(), ldh=h.stride(0),
+              h_dtype=_dt(h), dense=_ptr(dense), shared_gate=_ptr(shared_gate), ld_gate=shared_gate.stride(0) if shared_gate is not None else 0,
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def moe_sort(idx: torch.Tensor, experts: int):
+    """idx [rows, top] int32 -> (counts [experts], offsets [experts + 1], perm [rows * top], inv [rows * top]) int32, pairs grouped by
+    expert in row order."""
+    _need_cuda(idx)
+    rows, top = idx.shape
+    dev = idx.device
+    counts = torch.empty(experts, device=dev, dtype=torch.int32)
+    offsets = torch.empty(experts + 1, device=dev, dtype=torch.int32)
+    perm = torch.empty(rows * top, device=dev, dtype=torch.int32)
+    inv = torch.empty(rows * top, device=dev, dtype=torch.int32)
+    _lib.call("vy_moe_sort", "VyMoeSort", rows=rows, experts=experts, top=top, idx=idx.data_ptr(), counts=counts.data_ptr(),
+              offsets=offsets.data_ptr(), perm=perm.data_ptr(), inv=inv.data_ptr(), stream=_stream())
+    return counts, offsets, perm, inv
+
+
+def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int, out_dtype: torch.dtype) -> torch.Tensor:
+    _need_cuda(x, perm)
+    _rows2d(x, "moe_gather x")
+    out = torch.empty((perm.numel(), x.shape[1]), device=x.device, dtype=out_dtype)
+    _lib.call("vy_moe_gather", "VyMoeGather", n=perm.numel(), top=top, width=x.shape[1], perm=perm.data_ptr(), x=x.data_ptr(), ldx=x.stride(0),
+              x_dtype=_dt(x), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def moe_combine(part: torch.Tensor, inv: torch.Tensor, weight: torch.Tensor, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[row] = addend[row] + sum_k weight[row, k] * part[inv[row * top + k]] (fp32)."""
+    _need_cuda(part, inv, weight, addend)
+    _rows2d(part, "moe_combine part")
+    rows, top = weight.shape
+    out = torch.empty((rows, part.shape[1]), device=part.device, dtype=torch.float32)
+    _lib.call("vy_moe_combine", "VyMoeCombine", rows=rows, top=top, width=part.shape[1], inv=inv.data_ptr(), weight=weight.data_ptr(),
+              part=part.data_ptr(), ld_part=part.stride(0), part_dtype=_dt(part), addend=_ptr(addend),
+              ld_addend=addend.stride(0) if addend is not None else 0, addend_dtype=_dt(addend) if addend is not None else 0,
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
     return out
 
 

@@ -223,7 +223,9 @@ class HybridCacheManager:
     """Pages and state slots for a model whose layers declare `cache_specs()` (per layer, per mixer:
     {"pages": (kv_heads, dim, vdim) | None, "states": {name: per-slot shape}}). Attention mixers get pools
     [num_blocks, block_size, kv_heads, dim | vdim] addressed through each sequence's block list — the same page scheme as
-    PagedKVManager above; recurrent mixers get fp32 tensors [num_slots, *shape] addressed by the sequence's slot. Both
+    PagedKVManager above (vdim 0: one pool only, for mixers whose values are part of the key row); a mixer that declares
+    "pages_from": (layer, mixer) owns no pool and is handed the view of the mixer it names (layers that attend over another
+    layer's cached rows); recurrent mixers get fp32 tensors [num_slots, *shape] addressed by the sequence's slot. Both
     grow on demand, so `max_tokens` / `max_seqs` are sizing hints, not limits. A slot or page handed out again is not
     cleared: a sequence whose first position is 0 never reads what its slot held, and pages are written before they are
     read."""
@@ -234,6 +236,15 @@ class HybridCacheManager:
         self._specs = model.cache_specs()
         self.has_pages = any(s["pages"] for layer in self._specs for s in layer)
         self.views: List[List[LayerCacheView]] = [[LayerCacheView() for _ in layer] for layer in self._specs]
+        for li, layer in enumerate(self._specs):
+            for mi, spec in enumerate(layer):
+                src = spec.get("pages_from")
+                if src is None:
+                    continue
+                lj, mj = int(src[0]), int(src[1])
+                if not (0 <= lj < len(self._specs) and 0 <= mj < len(self._specs[lj]) and self._specs[lj][mj].get("pages")):
+                    raise ValueError(f"layer {li}: pages_from {src} does not name a mixer that owns pages")
+                self.views[li][mi] = self.views[lj][mj]   # the same object: growing the owner's pools is seen here too
         self.num_blocks = 0
         self.num_slots = 0
         self.generation = 0
@@ -252,6 +263,8 @@ class HybridCacheManager:
                 g, dk, dv = spec["pages"]
                 dt = spec.get("kv_dtype", torch.float32)
                 for name, d in (("k_pool", dk), ("v_pool", dv)):
+                    if d == 0:
+                        continue
                     new = torch.zeros((new_total, self.block_size, g, d), device=self.device, dtype=dt)
                     old = getattr(view, name)
                     if old is not None:

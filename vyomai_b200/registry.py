@@ -32,6 +32,11 @@ def _gelutar(path, **kw):
     return GelutarForCausalLM.from_pretrained(path, **kw)
 
 
+def _zugunex(path, **kw):
+    from .models.zugunex import ZugunexForCausalLM
+    return ZugunexForCausalLM.from_pretrained(path, **kw)
+
+
 def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
     """The RMSNorm / SwiGLU / RoPE decoder (models/custom_transformer.py): config.json holds its Config fields, the checkpoint
     its state_dict."""
@@ -46,4 +51,5 @@ def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
 
 
 register_model("Gelutar", _gelutar)
+register_model("Zugunex", _zugunex)
 register_model("ModelForCausalLM", _custom_lm)
