@@ -1079,6 +1079,172 @@ def run_hybrid(args):
                       "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
                       "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
 
+# ------------------------------------------------------------------------------------------------
+# --workload latent: the Zugunex latent-attention / mixture-of-experts decoder beside the Gelutar hybrid decoder at equal
+# width / depth / vocabulary (both run on HybridBatchEngine's packed step)
+# ------------------------------------------------------------------------------------------------
+LATENT_KERNELS = ("window_attn_tiled", "window_attn_decode", "window_attn", "latent_kv_write", "rope_split", "moe_route", "moe_scale", "moe_sort",
+                  "moe_gather", "moe_combine", "linear_tile", "linear_rows", "linear_attn_chunk", "linear_attn", "delta_rule", "delta_prep",
+                  "causal_conv", "rms_norm", "kv_page_write", "unary", "embed_rows", "gemm_skinny", "gemm_kernel", "argmax")
+
+
+def latent_config(width, layers=8, vocab=32768, window=512):
+    """A realistic layer stack: 64 + 32 query / key channels and 64 value channels per head, latent rank 192, every second layer
+    reading the latent rows of the layer before it, a dense tanh-GELU feed-forward (4 x width) in the first layer and 32 squared-ReLU
+    experts of width / 4 (4 chosen) plus a shared expert of width / 2 in the others."""
+    H = width // 64
+    def mix(i):
+        m = {"heads": H, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 192, "scale": 96 ** -0.5, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": 32}}
+        if i % 2:
+            m["kv_from"] = i - 1
+        return m
+    moe = {"kind": "moe", "expert": {"ff": width // 4}, "router": {"experts": 32, "top": 4, "scale": 2.5}, "shared": {"ff": width // 2}}
+    return {"architecture": "Zugunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": mix(i), "mlp": {"kind": "dense", "ff": 4 * width} if i == 0 else moe} for i in range(layers)]}
+
+
+def _packed_numbers(dev, model, vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup):
+    """Prefill and single-token-step timings of a packed-step model through HybridBatchEngine: prompts from pinned host ids inside the
+    timed region with L2 flushed between iterations; decode as CUDA-graph replays; CUPTI kernel tables of one prefill and one eager step."""
+    from vyomai_b200 import HybridBatchEngine, HybridCacheManager
+    g = torch.Generator().manual_seed(1)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    mgr = HybridCacheManager(model, max_tokens=batch_decode * (prompt + decode_steps + 16), block_size=16, max_seqs=batch_decode)
+    eng = HybridBatchEngine(model, mgr)
+    prompts = [torch.randint(0, vocab, (prompt,), generator=g).tolist() for _ in range(batch_decode)]
+    prefill = lambda n: eng.feed([(i, prompts[i], [prompt - 1]) for i in range(n)])  # noqa: E731
+    out, times = {}, []
+    for it in range(warmup + steps):
+        flush.fill_(it)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        prefill(batch_prefill)
+        e1.record()
+        torch.cuda.synchronize()
+        eng.release(range(batch_prefill))
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1))
+    pre_ms = sorted(times)[len(times) // 2]
+    out["prefill"] = {"batch": batch_prefill, "prompt": prompt, "ms": round(pre_ms, 3), "tok_per_s": round(batch_prefill * prompt / pre_ms * 1e3)}
+    out["prefill_kernels"] = _kernel_table(lambda: prefill(batch_prefill), LATENT_KERNELS)
+    eng.release(range(batch_prefill))
+    prefill(batch_decode)
+    nxt = [[int(t)] for t in torch.randint(0, vocab, (batch_decode,), generator=g)]
+    one = lambda: eng.feed([(i, nxt[i], [0]) for i in range(batch_decode)])  # noqa: E731
+    for _ in range(4):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(decode_steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    step_us = e0.elapsed_time(e1) * 1e3 / decode_steps
+    cap = next(iter(eng._graphs.values()), None)
+    dev_us = None
+    if cap is not None:
+        e0.record()
+        for _ in range(8):
+            cap.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        dev_us = e0.elapsed_time(e1) * 1e3 / 8
+    out["decode"] = {"batch": batch_decode, "context": prompt, "us_per_step_engine": round(step_us, 1), "us_per_step_device": dev_us and round(dev_us, 1),
+                     "tok_per_s": round(batch_decode / step_us * 1e6), "graph": cap is not None}
+    eng.use_graph = False
+    one()
+    out["decode_kernels_eager"] = _kernel_table(one, LATENT_KERNELS)
+    eng.release(range(batch_decode))
+    return out
+
+
+def measure_latent(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, decode_steps=64, steps=5, warmup=3):
+    from vyomai_b200 import GelutarConfig, GelutarForCausalLM, ZugunexConfig, ZugunexForCausalLM
+    hbm, _, _, src = peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    fp32_tflops = sms * 128 * 2 * 1.965e9 / 1e12
+    cfgd = latent_config(width)
+    cfg = ZugunexConfig(cfgd)
+    model = ZugunexForCausalLM(cfg, ZugunexForCausalLM.random_weights(cfg, seed=0), dtype=torch.bfloat16, device=dev)
+    out = {"width": width, "vocab": cfg.vocab, "peaks": src, "fp32_tflops_nominal": round(fp32_tflops, 1)}
+    z = _packed_numbers(dev, model, cfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup)
+    m = cfgd["layers"][0]["mixer"]
+    tokens, W = batch_prefill * prompt, m["mask"]["size"]
+    visible = sum(min(p + 1, W) for p in range(prompt)) / prompt
+    row = m["kv_rank"] + m["rot_dim"]
+    fl = len(cfgd["layers"]) * tokens * m["heads"] * visible * (row + m["kv_rank"]) * 2
+    ms = z["prefill_kernels"].get("window_attn_tiled", {}).get("ms")
+    if ms:
+        z["window_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
+    # single-token attention: the bytes of the visible latent rows, read once per (sequence, layer) if the heads share them through L2
+    ms = z["decode_kernels_eager"].get("window_attn_decode", {}).get("ms")
+    if ms:
+        by = len(cfgd["layers"]) * batch_decode * min(W, prompt) * row * 4
+        z["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "MB_per_head": round(by * m["heads"] / 1e6, 1),
+                                            "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
+                                            "frac_of_hbm_per_head": round(by * m["heads"] / (ms * 1e-3) / 1e9 / hbm, 3)}
+    step_bytes = 2.0 * sum(t.numel() for t in latent_weights(model)) + len(cfgd["layers"]) * batch_decode * min(W, prompt) * row * 4
+    if z["decode"]["us_per_step_device"]:
+        z["decode"].update(step_algorithmic_MB=round(step_bytes / 1e6, 1),
+                           hbm_frac_device=round(step_bytes / (z["decode"]["us_per_step_device"] * 1e-6) / 1e9 / hbm, 3))
+    out["zugunex"] = z
+    del model
+    torch.cuda.empty_cache()
+    gd = hybrid_config(width)
+    gcfg = GelutarConfig(gd)
+    gmodel = GelutarForCausalLM(gcfg, GelutarForCausalLM.random_weights(gcfg, seed=0, low_rank=64), dtype=torch.bfloat16, device=dev)
+    gz = _packed_numbers(dev, gmodel, gcfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup)
+    par = gd["layers"][3]["mixer"]["left"]
+    n_par = sum(1 for L in gd["layers"] if L["type"] == "parallel")
+    Wg, K = par["mask"]["size"], par["mask"]["keep_first"]
+    vis = sum(min(p + 1, Wg) + (min(K, p + 1 - Wg) if p + 1 > Wg else 0) for p in range(prompt)) / prompt
+    fl = n_par * tokens * par["heads"] * vis * (par["dim"] + par["vdim"]) * 2
+    ms = gz["prefill_kernels"].get("window_attn_tiled", {}).get("ms")
+    if ms:
+        gz["window_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
+    ms = gz["decode_kernels_eager"].get("window_attn_decode", {}).get("ms")
+    if ms:
+        by = n_par * batch_decode * (Wg + K) * par["kv_heads"] * (par["dim"] + par["vdim"]) * 4
+        gz["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3)}
+    out["gelutar"] = gz
+    del gmodel
+    torch.cuda.empty_cache()
+    return out
+
+
+def latent_weights(model):
+    """Every weight a Zugunex decode step reads (the all-experts form reads every expert once)."""
+    seen = []
+    for L in model.layers:
+        seen += [L.inp.weight, L.mixer.uk_t, L.mixer.uv, L.mixer.o.weight]
+        if L.mlp is not None:
+            seen += [L.mlp.up_all.weight, L.mlp.down_all.weight, L.mlp.router.weight] if L.moe else [L.mlp.up.weight, L.mlp.down.weight]
+    seen.append(model.head.weight)
+    return seen
+
+
+def run_latent(args):
+    from vyomai_b200 import _lib
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus != 1:
+        print(json.dumps({"workload": "latent", "error": "the latent-attention decoder measurement runs on one GPU"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.vy_launch_count()
+    res = [_guarded(measure_latent, dev, int(w), steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3)) for w in args.hybrid_sizes.split(",")]
+    launches = L.vy_launch_count() - n0
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    print(json.dumps({"workload": "latent", "metric": "zugunex_prefill_and_decode_tokens_per_s", "n_gpus": 1, "dtype": "bf16 (fp32 residual / scores / router)",
+                      "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
+                      "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -1087,12 +1253,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid"],
+    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid", "latent"],
                     help="package: VisionLanguageModel of the reference package (1 image token + 127 text, the headline); "
                          "slots: the notebook-II form (197 image tokens in a 248-token sequence); "
                          "hybrid: prefill / decode throughput of the Gelutar hybrid decoder beside DecoderModel at equal size (1 GPU, "
-                         "its own JSON line; not the headline metric)")
-    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid: model widths to measure")
+                         "its own JSON line; not the headline metric); "
+                         "latent: the same for the Zugunex latent-attention / mixture-of-experts decoder beside Gelutar at equal size")
+    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid / latent: model widths to measure")
     ap.add_argument("--no-configs-1-2", action="store_true", help="skip the encoder (C1) / ViT (C2) measurements appended at N = 1")
     ap.add_argument("--no-config5", action="store_true", help="skip the PaliGemma-scale prefill + decode measurement appended at N = 1")
     ap.add_argument("--no-slots", action="store_true", help="skip the notebook-II measurement appended at N = 1")
@@ -1109,6 +1276,8 @@ def main():
         run_reference(args)
     elif args.workload == "hybrid":
         run_hybrid(args)
+    elif args.workload == "latent":
+        run_latent(args)
     else:
         run_ours(args)
 

@@ -168,7 +168,7 @@ def test_router_ties_go_to_the_lowest_index():
 
 
 @pytest.mark.parametrize("shared_ff", [None, 20])
-@pytest.mark.parametrize("rows,sorted_min", [(1, 128), (7, 128), (40, 8), (300, 8)])
+@pytest.mark.parametrize("rows,sorted_min", [(1, 128), (7, 128), (20, 128), (40, 8), (300, 8)])
 def test_both_forms_of_the_experts_sum(rows, sorted_min, shared_ff):
     from vyomai_b200 import ops
     from vyomai_b200.layers.mixers import MoEFeedForward
@@ -187,7 +187,7 @@ def test_both_forms_of_the_experts_sum(rows, sorted_min, shared_ff):
     h = torch.randn(rows, width, generator=g)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
     batch = ops.PackedBatch(t([0, rows]), t([0]), t([0]), rows, None, 0)
-    got = mlp.forward(h.to(DEV), h.to(DEV), batch).cpu()
+    got = mlp.forward(h.to(DEV), batch).cpu()
     spec = U.moe(experts=E, top=top, ff=ff, scale=1.3, shared_ff=shared_ff)
     want = O.moe_ff(h.double(), {k: v.double() for k, v in w.items()}, spec)
     assert HU.rel_err(got, want) < 1e-5
@@ -210,7 +210,7 @@ def test_sorted_pairs_are_grouped_by_expert_in_row_order():
 def test_batched_per_head_product():
     from vyomai_b200 import ops
     g = torch.Generator().manual_seed(10)
-    for rows in (3, 50):
+    for rows in (3, 20, 50):
         x = torch.randn(rows, 4 * 7 + 2, generator=g)
         w = torch.randn(4, 5, 6, generator=g)
         out = torch.zeros(rows, 4 * 9, device=DEV)
@@ -232,3 +232,25 @@ def test_gelu_tanh_in_both_projection_arms():
     want_b = O.gelu_tanh(xb.double() @ wb.double().T)
     got16 = Projection(wb.to(DEV))(xb.to(DEV), act="gelu_tanh").cpu()
     assert HU.rel_err(got16, want_b) < 1e-3
+
+
+@pytest.mark.parametrize("dim,vdim,kv_heads", [(24, 16, 2), (22, 10, 1)])
+def test_single_token_attention_with_heads_grouped_per_cta(dim, vdim, kv_heads):
+    """Large single-token batches put four heads of one key / value head into a CTA; small ones one head per CTA (the form the
+    mixer tests hold against the oracle). Both must give the same numbers, through the 16-byte and the scalar loads."""
+    from vyomai_b200 import ops
+    H, n, bs = 8, 48, 4
+    g = torch.Generator().manual_seed(dim)
+    pos0 = torch.randint(0, 60, (n,), generator=g).tolist()
+    batch, table, _, n_blocks, _ = HU.shuffled_batch([1] * n, pos0, bs, DEV)
+    kp = torch.randn(n_blocks, bs, kv_heads, dim, generator=g).to(DEV)
+    vp = torch.randn(n_blocks, bs, kv_heads, vdim, generator=g).to(DEV)
+    q = torch.randn(n, H * dim, generator=g).to(DEV)
+    sink, gate = torch.randn(H, generator=g).to(DEV), torch.randn(n, H, generator=g).to(DEV)
+    kw = dict(heads=H, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=0.3, window=9, keep_first=0, sink=sink)
+    whole = ops.window_attn(batch, q, kp, vp, gate=gate, **kw)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+    for a in range(0, n, 8):
+        sub = ops.PackedBatch(t(list(range(9))), t(pos0[a:a + 8]), t([0] * 8), 1, batch.block_table[a:a + 8].contiguous(), bs)
+        part = ops.window_attn(sub, q[a:a + 8], kp, vp, gate=gate[a:a + 8], **kw)
+        assert float((part - whole[a:a + 8]).abs().max()) < 1e-5

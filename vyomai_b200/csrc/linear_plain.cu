@@ -1,6 +1,7 @@
 // vy_linear_plain: out = act(A W^T + bias) * scale + addend for any M, N, K and any alignment, fp32 FMA accumulation.
-// Two kernels: 64 x 64 x 16 shared-memory tiles (4 x 4 outputs per thread) for many rows, and a weight-streaming kernel
-// (one warp per output feature, lanes over K) for at most 8 rows. This is the exact-fp32 arm of every projection of the
+// Three kernels: 64 x 64 x 16 shared-memory tiles (4 x 4 outputs per thread) for many rows, a weight-streaming kernel
+// (one warp per output feature, lanes over K) for at most 8 rows, and a 32-feature tile for 9 .. 32 rows. A call may hold a batch
+// of independent products of one shape (blockIdx z / y picks the product). This is the exact-fp32 arm of every projection of the
 // sequence-mixer models and the bf16 arm of the shapes the tensor-core GEMM does not take (a contraction over a
 // low rank, a handful of output features, strides that are not 16-byte multiples). vy_unary and vy_embed_rows live
 // here as well.
@@ -115,6 +116,49 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinDev d) {
   }
 }
 
+// 9 .. 32 rows (a decode batch; the per-head products of latent attention): a CTA takes 32 output features of one product, thread
+// (feature, group of 4 rows); A and W pass through shared memory 64 k at a time, W transposed so that a warp's features are adjacent
+constexpr int LS_N = 32, LS_K = 64, LS_M = 32;
+__global__ void __launch_bounds__(256) linear_small_kernel(LinDev d) {
+  pdl_trigger();
+  pdl_wait();
+  lin_select(d, blockIdx.y);
+  __shared__ __align__(16) float xs[LS_M][LS_K + 4];
+  __shared__ float ws[LS_K][LS_N + 1];
+  const int t = threadIdx.x, n = t & 31, mg = t >> 5;
+  const int n0 = blockIdx.x * LS_N;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < d.K; k0 += LS_K) {
+    {
+      const int r = t >> 3, kk = (t & 7) * 8;   // 32 rows x 8 threads x 8 k
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + kk + j;
+        xs[r][kk + j] = (r < d.M && k < d.K) ? ld_as_float(d.A, d.a_dt, static_cast<long long>(r) * d.lda + k) : 0.f;
+        ws[kk + j][r] = (n0 + r < d.N && k < d.K) ? ld_as_float(d.W, d.w_dt, static_cast<long long>(n0 + r) * d.ldw + k) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < LS_K; k += 4) {
+      const float w0 = ws[k][n], w1 = ws[k + 1][n], w2 = ws[k + 2][n], w3 = ws[k + 3][n];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 x = *reinterpret_cast<const float4*>(&xs[4 * mg + i][k]);
+        acc[i] = fmaf(x.x, w0, acc[i]);
+        acc[i] = fmaf(x.y, w1, acc[i]);
+        acc[i] = fmaf(x.z, w2, acc[i]);
+        acc[i] = fmaf(x.w, w3, acc[i]);
+      }
+    }
+    __syncthreads();
+  }
+  if (n0 + n < d.N)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (4 * mg + i < d.M) lin_store(d, 4 * mg + i, n0 + n, acc[i]);
+}
+
 __global__ void __launch_bounds__(256) unary_kernel(long long rows, int cols, const void* x, long long ldx, int x_dt, int act,
                                                      void* out, long long ld_out, int out_dt) {
   pdl_trigger();
@@ -171,6 +215,8 @@ extern "C" int vy_linear_plain(const VyLinear* p) {
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   if (p->M <= 8) {
     VY_CUDA_OK(launch_kernel(linear_rows_kernel, dim3((p->N + 7) / 8, batch), dim3(256), 0, st, d));
+  } else if (p->M <= LS_M) {
+    VY_CUDA_OK(launch_kernel(linear_small_kernel, dim3((p->N + LS_N - 1) / LS_N, batch), dim3(256), 0, st, d));
   } else {
     VY_CHECK_ARG((p->M + LT - 1) / LT <= 65535, "vy_linear_plain: too many rows (%d)", p->M);
     VY_CUDA_OK(launch_kernel(linear_tile_kernel, dim3((p->N + LT - 1) / LT, (p->M + LT - 1) / LT, batch), dim3(256), 0, st, d));

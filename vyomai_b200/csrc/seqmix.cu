@@ -289,49 +289,59 @@ constexpr int WD_WARPS = 8;
 constexpr int WD_KEYS = 4;
 
 // VEC: fp32 pages and query, dim and vdim multiples of 4, 16-byte aligned rows: lane l holds channels 4 l .. 4 l + 3 (+ 128) and
-// reads a key or value row with one 16-byte load per 128 channels instead of four 4-byte ones
-template <bool VEC>
+// reads a key or value row with one 16-byte load per 128 channels instead of four 4-byte ones.
+// HG: query heads per CTA, all reading the same key / value head (grouped heads; the single head of latent rows): a key or value
+// row is loaded once and used by the HG heads, so the pages cross L2 heads / HG times instead of heads times
+template <bool VEC, int HG>
 __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDev d) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float wa_smem[];
-  const int s = blockIdx.z, h = blockIdx.y;
+  const int s = blockIdx.z, h0 = blockIdx.y * HG;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int base = d.cu[s];
   if (d.cu[s + 1] - base <= 0) return;
-  const int g = h / (d.heads / d.kv_heads);
+  const int g = h0 / (d.heads / d.kv_heads);
   const long long qrow = base;
   // channel of register slot r: strided by 32 (scalar form) or groups of 4 strided by 128 (vector form)
   auto chan = [&](int r) { return VEC ? 4 * lane + 128 * (r >> 2) + (r & 3) : lane + 32 * r; };
-  float qreg[WA_VR];
+  float qreg[HG][WA_VR];
 #pragma unroll
-  for (int r = 0; r < WA_VR; ++r) {
-    const int col = chan(r);
-    qreg[r] = col < d.dim ? ld_as_float(d.q, d.q_dt, qrow * d.ldq + static_cast<long long>(h) * d.dim + col) * d.scale : 0.f;
-  }
+  for (int hh = 0; hh < HG; ++hh)
+#pragma unroll
+    for (int r = 0; r < WA_VR; ++r) {
+      const int col = chan(r);
+      qreg[hh][r] = col < d.dim ? ld_as_float(d.q, d.q_dt, qrow * d.ldq + static_cast<long long>(h0 + hh) * d.dim + col) * d.scale : 0.f;
+    }
   const int pos = d.pos0[s];
   const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
   const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
   const int count = nA + (pos + 1 - lowB);
-  float m = -INFINITY, l = 0.f;
-  if (d.sink && warp == 0) {
-    m = ld_as_float(d.sink, d.sink_dt, h);
-    l = 1.f;
-  }
-  float acc[WA_VR];
+  float m[HG], l[HG];
+  float acc[HG][WA_VR];
 #pragma unroll
-  for (int r = 0; r < WA_VR; ++r) acc[r] = 0.f;
+  for (int hh = 0; hh < HG; ++hh) {
+    m[hh] = -INFINITY;
+    l[hh] = 0.f;
+    if (d.sink && warp == 0) {
+      m[hh] = ld_as_float(d.sink, d.sink_dt, h0 + hh);
+      l[hh] = 1.f;
+    }
+#pragma unroll
+    for (int r = 0; r < WA_VR; ++r) acc[hh][r] = 0.f;
+  }
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
   const long long kstride = d.k_row, vstride = d.v_row;
   for (int c0 = WD_KEYS * warp; c0 < count; c0 += WD_KEYS * WD_WARPS) {
     long long row[WD_KEYS];
-    float sc[WD_KEYS], vv[WD_KEYS][WA_VR];
+    float sc[HG][WD_KEYS], vv[WD_KEYS][WA_VR];
 #pragma unroll
     for (int u = 0; u < WD_KEYS; ++u) {
       const int c = min(c0 + u, count - 1);   // past the end: a repeat of the last key, given weight 0 below
       const int kp = c < nA ? c : lowB + (c - nA);
       row[u] = static_cast<long long>(tab[kp / d.bs]) * d.bs + kp % d.bs;
-      sc[u] = 0.f;
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) sc[hh][u] = 0.f;
     }
     if constexpr (VEC) {
       const float* kb = reinterpret_cast<const float*>(d.kp) + static_cast<long long>(g) * d.dim + 4 * lane;
@@ -342,10 +352,13 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
 #pragma unroll
           for (int u = 0; u < WD_KEYS; ++u) {
             const float4 k4 = *reinterpret_cast<const float4*>(kb + row[u] * kstride + 128 * r4);
-            sc[u] = fmaf(qreg[4 * r4], k4.x, sc[u]);
-            sc[u] = fmaf(qreg[4 * r4 + 1], k4.y, sc[u]);
-            sc[u] = fmaf(qreg[4 * r4 + 2], k4.z, sc[u]);
-            sc[u] = fmaf(qreg[4 * r4 + 3], k4.w, sc[u]);
+#pragma unroll
+            for (int hh = 0; hh < HG; ++hh) {
+              sc[hh][u] = fmaf(qreg[hh][4 * r4], k4.x, sc[hh][u]);
+              sc[hh][u] = fmaf(qreg[hh][4 * r4 + 1], k4.y, sc[hh][u]);
+              sc[hh][u] = fmaf(qreg[hh][4 * r4 + 2], k4.z, sc[hh][u]);
+              sc[hh][u] = fmaf(qreg[hh][4 * r4 + 3], k4.w, sc[hh][u]);
+            }
           }
         }
       }
@@ -364,8 +377,11 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
         const int col = lane + 32 * r;
         if (col < d.dim) {
 #pragma unroll
-          for (int u = 0; u < WD_KEYS; ++u)
-            sc[u] = fmaf(qreg[r], ld_as_float(d.kp, d.pool_dt, row[u] * kstride + static_cast<long long>(g) * d.dim + col), sc[u]);
+          for (int u = 0; u < WD_KEYS; ++u) {
+            const float kv = ld_as_float(d.kp, d.pool_dt, row[u] * kstride + static_cast<long long>(g) * d.dim + col);
+#pragma unroll
+            for (int hh = 0; hh < HG; ++hh) sc[hh][u] = fmaf(qreg[hh][r], kv, sc[hh][u]);
+          }
         }
       }
 #pragma unroll
@@ -376,50 +392,57 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
           vv[u][r] = col < d.vdim ? ld_as_float(d.vp, d.pool_dt, row[u] * vstride + static_cast<long long>(g) * d.vdim + col) : 0.f;
       }
     }
-    float m_new = m;
 #pragma unroll
-    for (int u = 0; u < WD_KEYS; ++u) {
-      sc[u] = c0 + u < count ? warp_sum(sc[u]) : -INFINITY;
-      m_new = fmaxf(m_new, sc[u]);
-    }
-    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
-    float p[WD_KEYS], ps = 0.f;
+    for (int hh = 0; hh < HG; ++hh) {
+      float m_new = m[hh];
 #pragma unroll
-    for (int u = 0; u < WD_KEYS; ++u) {
-      p[u] = c0 + u < count ? expf(sc[u] - m_new) : 0.f;
-      ps += p[u];
+      for (int u = 0; u < WD_KEYS; ++u) {
+        sc[hh][u] = c0 + u < count ? warp_sum(sc[hh][u]) : -INFINITY;
+        m_new = fmaxf(m_new, sc[hh][u]);
+      }
+      const float corr = m[hh] == -INFINITY ? 0.f : expf(m[hh] - m_new);
+      float p[WD_KEYS], ps = 0.f;
+#pragma unroll
+      for (int u = 0; u < WD_KEYS; ++u) {
+        p[u] = c0 + u < count ? expf(sc[hh][u] - m_new) : 0.f;
+        ps += p[u];
+      }
+      l[hh] = fmaf(l[hh], corr, ps);
+      m[hh] = m_new;
+#pragma unroll
+      for (int r = 0; r < WA_VR; ++r) {
+        float a = acc[hh][r] * corr;
+#pragma unroll
+        for (int u = 0; u < WD_KEYS; ++u) a = fmaf(p[u], vv[u][r], a);
+        acc[hh][r] = a;
+      }
     }
-    l = fmaf(l, corr, ps);
-    m = m_new;
+  }
+  float* ms = wa_smem;                          // [HG][WD_WARPS]
+  float* ls = ms + HG * WD_WARPS;               // [HG][WD_WARPS]
+  float* as = ls + HG * WD_WARPS;               // [HG][WD_WARPS][vdim]
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) {
+    if (lane == 0) { ms[hh * WD_WARPS + warp] = m[hh]; ls[hh * WD_WARPS + warp] = l[hh]; }
 #pragma unroll
     for (int r = 0; r < WA_VR; ++r) {
-      float a = acc[r] * corr;
-#pragma unroll
-      for (int u = 0; u < WD_KEYS; ++u) a = fmaf(p[u], vv[u][r], a);
-      acc[r] = a;
+      const int col = chan(r);
+      if (col < d.vdim) as[(hh * WD_WARPS + warp) * d.vdim + col] = acc[hh][r];
     }
   }
-  float* ms = wa_smem;                          // [WD_WARPS]
-  float* ls = ms + WD_WARPS;                    // [WD_WARPS]
-  float* as = ls + WD_WARPS;                    // [WD_WARPS][vdim]
-  if (lane == 0) { ms[warp] = m; ls[warp] = l; }
-#pragma unroll
-  for (int r = 0; r < WA_VR; ++r) {
-    const int col = chan(r);
-    if (col < d.vdim) as[warp * d.vdim + col] = acc[r];
-  }
   __syncthreads();
-  if (warp != 0) return;
-  float M = ms[0];
-  for (int w = 1; w < WD_WARPS; ++w) M = fmaxf(M, ms[w]);
-  l = 0.f;
+  if (warp >= HG) return;   // warp w merges head h0 + w (HG <= WD_WARPS)
+  const int hh = warp, h = h0 + hh;
+  float M = ms[hh * WD_WARPS];
+  for (int w = 1; w < WD_WARPS; ++w) M = fmaxf(M, ms[hh * WD_WARPS + w]);
+  float lt = 0.f;
   float wgt[WD_WARPS];
 #pragma unroll
   for (int w = 0; w < WD_WARPS; ++w) {
-    wgt[w] = ms[w] == -INFINITY ? 0.f : expf(ms[w] - M);
-    l = fmaf(ls[w], wgt[w], l);
+    wgt[w] = ms[hh * WD_WARPS + w] == -INFINITY ? 0.f : expf(ms[hh * WD_WARPS + w] - M);
+    lt = fmaf(ls[hh * WD_WARPS + w], wgt[w], lt);
   }
-  float og = 1.f / l;
+  float og = 1.f / lt;
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
@@ -427,7 +450,7 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
     if (col < d.vdim) {
       float a = 0.f;
 #pragma unroll
-      for (int w = 0; w < WD_WARPS; ++w) a = fmaf(as[w * d.vdim + col], wgt[w], a);
+      for (int w = 0; w < WD_WARPS; ++w) a = fmaf(as[(hh * WD_WARPS + w) * d.vdim + col], wgt[w], a);
       st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, a * og);
     }
   }
@@ -849,11 +872,18 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
   if (p->max_new >= WA_TILED_MIN) {   // prompt-sized: 64 x 64 register-tiled form
     VY_CUDA_OK(launch_window_attn_tiled(d, p->n_seqs, p->max_new, st));
   } else if (p->max_new == 1) {
-    const size_t smem = sizeof(float) * (2 * WD_WARPS + static_cast<size_t>(WD_WARPS) * p->vdim);
     const auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
     const bool vec = p->pool_dtype == VY_F32 && p->dim % 4 == 0 && p->vdim % 4 == 0 && d.k_row % 4 == 0 && d.v_row % 4 == 0 && al(p->k_pool) && al(p->v_pool);
-    VY_CUDA_OK(vec ? launch_kernel(window_attn_decode_kernel<true>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d)
-                   : launch_kernel(window_attn_decode_kernel<false>, dim3(1, p->heads, p->n_seqs), dim3(WD_WARPS * 32), smem, st, d));
+    // four heads of one key / value head per CTA while that still leaves a CTA for most SMs; else one head per CTA
+    const int per_kv = p->heads / p->kv_heads;
+    const bool grouped = per_kv % 4 == 0 && static_cast<long long>(p->heads / 4) * p->n_seqs >= 96;
+    const int hg = grouped ? 4 : 1;
+    const size_t smem = sizeof(float) * hg * (2 * WD_WARPS + static_cast<size_t>(WD_WARPS) * p->vdim);
+    const dim3 grid(1, p->heads / hg, p->n_seqs), block(WD_WARPS * 32);
+    VY_CUDA_OK(grouped ? (vec ? launch_kernel(window_attn_decode_kernel<true, 4>, grid, block, smem, st, d)
+                              : launch_kernel(window_attn_decode_kernel<false, 4>, grid, block, smem, st, d))
+                       : (vec ? launch_kernel(window_attn_decode_kernel<true, 1>, grid, block, smem, st, d)
+                              : launch_kernel(window_attn_decode_kernel<false, 1>, grid, block, smem, st, d)));
   } else {
     const size_t smem = sizeof(float) * static_cast<size_t>(WA_WARPS) * p->dim;
     VY_CUDA_OK(launch_kernel(window_attn_kernel, dim3((p->max_new + WA_WARPS - 1) / WA_WARPS, p->heads, p->n_seqs), dim3(WA_WARPS * 32), smem,

@@ -288,7 +288,8 @@ class ReluSquaredMLP(DenseMLP):
 class MoEFeedForward:
     """Mixture of experts W_down_e act(W_up_e h) with a sigmoid router: the `top` largest scores are kept, divided by their sum
     and multiplied by `route_scale`; an optional shared expert runs for every token, times sigmoid(w_sg . h). Router logits and
-    the shared gate are one fp32 product read from the fp32 layer input.
+    the shared gate are one product with fp32 accumulation and an fp32 result (its input is the layer input as the experts read
+    it: bf16-rounded when the model's projections are); scores, selection and weights are fp32.
 
     Two exact forms of the same sum. Single tokens and short steps (also every CUDA-graph-captured step: no host decision)
     run ALL experts as two products over the concatenated experts, the hidden activations multiplied by each token's routing
@@ -314,7 +315,7 @@ class MoEFeedForward:
         up_all = torch.cat(ups, 0).contiguous()        # [E ff + S, W]
         down_all = torch.cat(downs, 1).contiguous()    # [W, E ff + S]
         self.up_all, self.down_all = Projection(up_all, tensor_cores), Projection(down_all, tensor_cores)
-        self.router = torch.cat(rt, 0).contiguous()    # [E (+ 1), W]: fp32 FMA against the fp32 layer input
+        self.router = Projection(torch.cat(rt, 0).contiguous(), tensor_cores)    # [E (+ 1), W]
         f = self.ff
         self.up_e = [Projection(up_all[e * f:(e + 1) * f], tensor_cores) for e in range(E)]
         self.down_e = [Projection(down_all[:, e * f:(e + 1) * f], tensor_cores) for e in range(E)]
@@ -322,10 +323,10 @@ class MoEFeedForward:
             self.up_s = Projection(up_all[E * f:], tensor_cores)
             self.down_s = Projection(down_all[:, E * f:], tensor_cores)
 
-    def forward(self, h: torch.Tensor, x32: torch.Tensor, batch) -> torch.Tensor:
-        """h: the layer input in the activation dtype, x32: the same rows in fp32 (router input). Returns fp32 [rows, width]."""
+    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
+        """h: the layer input in the activation dtype. Returns fp32 [rows, width]."""
         E, rows = self.experts, h.shape[0]
-        z = ops.linear_plain(x32, self.router, out_dtype=torch.float32)
+        z = self.router(h)
         sorted_form = batch.max_new > 1 and rows >= self.sorted_min_rows
         idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form)
         sg = z[:, E:E + 1] if self.shared_ff else None

@@ -124,7 +124,7 @@ class _Layer:
         ops.rms_norm(y, self.norm1, eps=self.eps, w_mode="plain", accumulate=True, out=x)
         if self.mlp is not None:
             h = self._act(x)
-            y = self.mlp.forward(h, x, batch) if self.moe else self.mlp.forward(h)
+            y = self.mlp.forward(h, batch) if self.moe else self.mlp.forward(h)
             ops.rms_norm(y, self.norm2, eps=self.eps, w_mode="plain", accumulate=True, out=x)
 
 
