@@ -1175,7 +1175,8 @@ def measure_latent(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, de
     tokens, W = batch_prefill * prompt, m["mask"]["size"]
     visible = sum(min(p + 1, W) for p in range(prompt)) / prompt
     row = m["kv_rank"] + m["rot_dim"]
-    fl = len(cfgd["layers"]) * tokens * m["heads"] * visible * (row + m["kv_rank"]) * 2
+    # whole prompts attend over per-head expanded keys / values: dim + rot_dim and vdim channels per (query, key, head)
+    fl = len(cfgd["layers"]) * tokens * m["heads"] * visible * (m["dim"] + m["rot_dim"] + m["vdim"]) * 2
     ms = z["prefill_kernels"].get("window_attn_tiled", {}).get("ms")
     if ms:
         z["window_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
@@ -1183,9 +1184,10 @@ def measure_latent(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, de
     ms = z["decode_kernels_eager"].get("window_attn_decode", {}).get("ms")
     if ms:
         by = len(cfgd["layers"]) * batch_decode * min(W, prompt) * row * 4
-        z["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "MB_per_head": round(by * m["heads"] / 1e6, 1),
-                                            "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
-                                            "frac_of_hbm_per_head": round(by * m["heads"] / (ms * 1e-3) / 1e9 / hbm, 3)}
+        dfl = len(cfgd["layers"]) * batch_decode * m["heads"] * min(W, prompt) * (row + m["kv_rank"]) * 2
+        z["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
+                                            "gflop": round(dfl / 1e9, 2), "tflops": round(dfl / ms / 1e9, 2),
+                                            "frac_of_fp32_nominal": round(dfl / ms / 1e9 / fp32_tflops, 3)}
     step_bytes = 2.0 * sum(t.numel() for t in latent_weights(model)) + len(cfgd["layers"]) * batch_decode * min(W, prompt) * row * 4
     if z["decode"]["us_per_step_device"]:
         z["decode"].update(step_algorithmic_MB=round(step_bytes / 1e6, 1),
@@ -1208,7 +1210,10 @@ def measure_latent(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, de
     ms = gz["decode_kernels_eager"].get("window_attn_decode", {}).get("ms")
     if ms:
         by = n_par * batch_decode * (Wg + K) * par["kv_heads"] * (par["dim"] + par["vdim"]) * 4
-        gz["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3)}
+        dfl = n_par * batch_decode * par["heads"] * (Wg + K) * (par["dim"] + par["vdim"]) * 2
+        gz["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
+                                             "gflop": round(dfl / 1e9, 2), "tflops": round(dfl / ms / 1e9, 2),
+                                             "frac_of_fp32_nominal": round(dfl / ms / 1e9 / fp32_tflops, 3)}
     out["gelutar"] = gz
     del gmodel
     torch.cuda.empty_cache()

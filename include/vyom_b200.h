@@ -793,6 +793,8 @@ typedef struct VyLatentWrite {
   const void* weight; int32_t w_dtype;
   float eps;
   void* pool; int64_t pool_row; int32_t pool_dtype;
+  /* optional: the same rows also written packed, copy[token * ld_copy + ..] (the step's own rows as a product's input) */
+  void* copy; int64_t ld_copy; int32_t copy_dtype;
   void* stream;
 } VyLatentWrite;
 VY_API int vy_latent_kv_write(const VyLatentWrite* p);

@@ -92,7 +92,7 @@ def _mixer(cfg_m, seed, dtype=torch.float32, shared_from=None, width=40):
     return mix, {k: v.double() for k, v in w.items()}
 
 
-def _run_mixer(mix, W, h, lengths_by_step, bs=4):
+def _run_mixer(mix, W, h, lengths_by_step, bs=4, expanded=None):
     """Feeds h [T, width] (one sequence) to the mixer in portions through real pages; returns [T, width]."""
     from vyomai_b200 import ops
     from vyomai_b200.paged import LayerCacheView
@@ -107,7 +107,7 @@ def _run_mixer(mix, W, h, lengths_by_step, bs=4):
         batch = ops.PackedBatch(t([0, n]), t([at]), t([0]), n, t(order).view(1, -1), bs)
         x = h[at:at + n].to(DEV)
         parts = [ops.linear_plain(x, wt.to(DEV).float()) for wt in mix.input_weights()]
-        outs.append(mix.forward(parts, batch, view).float().cpu())
+        outs.append(mix.forward(parts, batch, view, expanded=expanded if at == 0 else False).float().cpu())
         at += n
     return torch.cat(outs)
 
@@ -121,6 +121,24 @@ def test_latent_attention_mixer(steps):
     want = O.latent_attention(h.double(), W, m, c, kr)
     got = _run_mixer(mix, W, h, steps)
     assert HU.rel_err(got, want) < 1e-4
+
+
+@pytest.mark.parametrize("window", [7, 16, 40])
+def test_whole_prompt_form_equals_the_latent_form(window):
+    """bf16 projections: a prompt from position 0 expands keys and values per head; portions and single tokens attend over latent
+    rows. Same sum, against the oracle and against each other; the rows must also be in the pages for what follows."""
+    m = U.attn(heads=4, dim=32, rot_dim=16, vdim=24, rank=48, window=window, scale=0.2)
+    mix, W = _mixer(m, 8, dtype=torch.bfloat16, width=64)
+    assert mix.expand is not None
+    h = torch.randn(37, 64, generator=torch.Generator().manual_seed(9))
+    c, kr = O.latent_kv(h.double(), W, m, 1e-5)
+    want = O.latent_attention(h.double(), W, m, c, kr)
+    latent = _run_mixer(mix, W, h, [37], expanded=False)
+    whole = _run_mixer(mix, W, h, [37], expanded=True)
+    then_decode = _run_mixer(mix, W, h, [30, 1, 1, 5], expanded=True)
+    for got in (latent, whole, then_decode):
+        assert HU.rel_err(got, want) < 2e-2
+    assert HU.rel_err(whole, latent) < 2e-2 and HU.rel_err(then_decode[30:], latent[30:]) < 2e-2
 
 
 def test_one_far_key_just_inside_the_window_dominates():
@@ -183,7 +201,7 @@ def test_both_forms_of_the_experts_sum(rows, sorted_min, shared_ff):
         w["shared.up"] = (torch.randn(shared_ff, width, generator=g) / math.sqrt(width)).to(torch.bfloat16)
         w["shared.down"] = (torch.randn(width, shared_ff, generator=g) / math.sqrt(shared_ff)).to(torch.bfloat16)
         w["shared.sg"] = torch.randn(1, width, generator=g).to(torch.bfloat16)
-    mlp = MoEFeedForward({k: v.to(DEV).float() for k, v in w.items()}, E, top, 1.3, torch.float32, True, shared=bool(shared_ff), sorted_min_rows=sorted_min)
+    mlp = MoEFeedForward({k: v.to(DEV).float() for k, v in w.items()}, E, top, 1.3, torch.float32, True, shared=bool(shared_ff), sorted_min_rows=sorted_min, force_sorted=True)
     h = torch.randn(rows, width, generator=g)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
     batch = ops.PackedBatch(t([0, rows]), t([0]), t([0]), rows, None, 0)
@@ -191,6 +209,20 @@ def test_both_forms_of_the_experts_sum(rows, sorted_min, shared_ff):
     spec = U.moe(experts=E, top=top, ff=ff, scale=1.3, shared_ff=shared_ff)
     want = O.moe_ff(h.double(), {k: v.double() for k, v in w.items()}, spec)
     assert HU.rel_err(got, want) < 1e-5
+
+
+def test_the_form_is_chosen_by_estimated_time():
+    """Narrow experts on the tensor cores: launches dominate, all experts at once; wide ones or fp32 FMA products: the sorted form."""
+    from vyomai_b200.layers.mixers import MoEFeedForward
+
+    def mlp(width, ff, dtype):
+        w = {"router": torch.zeros(32, width, dtype=dtype, device=DEV)}
+        for e in range(32):
+            w[f"e{e}.up"], w[f"e{e}.down"] = torch.zeros(ff, width, dtype=dtype, device=DEV), torch.zeros(width, ff, dtype=dtype, device=DEV)
+        return MoEFeedForward(w, 32, 4, 1.0, dtype, True)
+    assert not mlp(256, 64, torch.bfloat16)._sorted_is_faster(8192)
+    assert mlp(2048, 1024, torch.bfloat16)._sorted_is_faster(8192)
+    assert mlp(256, 64, torch.float32)._sorted_is_faster(8192)
 
 
 def test_sorted_pairs_are_grouped_by_expert_in_row_order():

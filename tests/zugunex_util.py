@@ -66,4 +66,5 @@ def build(cfg_dict: dict, dtype=torch.float32, seed=0, weights=None, **kw):
     cfg = ZugunexConfig(cfg_dict)
     w = weights if weights is not None else ZugunexForCausalLM.random_weights(cfg, seed=seed)
     kw.setdefault("sorted_min_rows", 8)   # both forms of the experts' sum come up at test sizes
+    kw.setdefault("force_sorted", True)
     return ZugunexForCausalLM(cfg, w, dtype=dtype, device="cuda", **kw), f64(w)

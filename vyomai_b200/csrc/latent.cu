@@ -27,7 +27,13 @@ struct LatDev {
   const void* w; int w_dt;
   float eps;
   void* pool; long long pool_row; int pool_dt;
+  void* copy; long long ld_copy; int copy_dt;
 };
+
+__device__ __forceinline__ void lat_store(const LatDev& d, long long po, long long co, int c, float v) {
+  st_from_float(d.pool, d.pool_dt, po + c, v);
+  if (d.copy) st_from_float(d.copy, d.copy_dt, co + c, v);
+}
 
 // one warp per token
 __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatDev d) {
@@ -39,7 +45,7 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatDev d) {
   for (int i = blockIdx.x * 4 + warp; i < n; i += gridDim.x * 4) {
     const int pos = d.pos0[s] + i;
     const long long row = static_cast<long long>(d.table[static_cast<long long>(s) * d.tw + pos / d.bs]) * d.bs + pos % d.bs;
-    const long long xo = static_cast<long long>(base + i) * d.ldx, po = row * d.pool_row;
+    const long long xo = static_cast<long long>(base + i) * d.ldx, po = row * d.pool_row, co = static_cast<long long>(base + i) * d.ld_copy;
     float ss = 0.f;
     for (int c = lane; c < d.rank; c += 32) {
       const float v = ld_as_float(d.x, d.x_dt, xo + c);
@@ -48,14 +54,14 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatDev d) {
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / static_cast<float>(d.rank) + d.eps);
     for (int c = lane; c < d.rank; c += 32)
-      st_from_float(d.pool, d.pool_dt, po + c, ld_as_float(d.x, d.x_dt, xo + c) * inv * ld_as_float(d.w, d.w_dt, c));
+      lat_store(d, po, co, c, ld_as_float(d.x, d.x_dt, xo + c) * inv * ld_as_float(d.w, d.w_dt, c));
     for (int pr = lane; 2 * pr < d.rot_dim; pr += 32) {
       float u = ld_as_float(d.x, d.x_dt, xo + d.rank + 2 * pr);
       const bool has_v = 2 * pr + 1 < d.rot_dim;
       float v = has_v ? ld_as_float(d.x, d.x_dt, xo + d.rank + 2 * pr + 1) : 0.f;
       if (2 * pr + 1 < d.rot_dims) rotate_pair(u, v, pos, d.inv_freq[pr]);
-      st_from_float(d.pool, d.pool_dt, po + d.rank + 2 * pr, u);
-      if (has_v) st_from_float(d.pool, d.pool_dt, po + d.rank + 2 * pr + 1, v);
+      lat_store(d, po, co, d.rank + 2 * pr, u);
+      if (has_v) lat_store(d, po, co, d.rank + 2 * pr + 1, v);
     }
   }
 }
@@ -301,6 +307,8 @@ extern "C" int vy_latent_kv_write(const VyLatentWrite* p) {
   d.inv_freq = p->inv_freq;
   d.w = p->weight; d.w_dt = p->w_dtype; d.eps = p->eps;
   d.pool = p->pool; d.pool_row = p->pool_row; d.pool_dt = p->pool_dtype;
+  VY_CHECK_ARG(!p->copy || (dtype_ok(p->copy_dtype) && p->ld_copy >= p->rank + p->rot_dim), "vy_latent_kv_write: bad copy");
+  d.copy = p->copy; d.ld_copy = p->ld_copy; d.copy_dt = p->copy_dtype;
   const int gx = (p->max_new + 3) / 4 < 4096 ? (p->max_new + 3) / 4 : 4096;
   VY_CUDA_OK(launch_kernel(latent_kv_write_kernel, dim3(gx, p->n_seqs), dim3(128), 0, static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();

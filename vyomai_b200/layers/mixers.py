@@ -192,7 +192,13 @@ class LatentAttention(Mixer):
     space once per token (qa_h = W_uk_h^T qn_h) and the attention runs with ONE key/value head over rows [c | kr] (key = the whole
     row, value = its first `rank` entries, both views of one pool), followed by the per-head value expansion. Pair rotation by
     position on the rotated parts, sliding window, softmax sink and sigmoid output gate as in WindowSinkAttention. A mixer built
-    with `shared_from` owns no down-projection: it reads the pool of the layer it names with its own W_uk / W_uv / queries."""
+    with `shared_from` owns no down-projection: it reads the pool of the layer it names with its own W_uk / W_uv / queries.
+
+    Whole prompts (every sequence of the step at position 0, bf16 projections) take the expanded form instead: nothing older
+    than the step is visible, so the step's own rows [c | kr] (written packed beside the pages) are expanded by ONE tensor-core
+    product against [W_uk_h 0; 0 I] per head and [W_uv 0] into per-head keys [kn_h | kr] and values, and the windowed attention
+    runs over that buffer with dim + rot_dim / vdim channels per head (2.6 x fewer fp32 multiply-adds than latent rows at
+    64 + 32 / 64 channels against rank 192) and no per-head products. Both forms are the same sum."""
 
     def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool,
                  kv_dtype: torch.dtype = torch.float32, shared_from: Optional[int] = None):
@@ -220,6 +226,15 @@ class LatentAttention(Mixer):
         self.uv = w["uv"].view(H, dv, R).contiguous()                       # [H, dv, R]
         self.sink = w["sink"].contiguous() if "sink" in w else None
         self.o = Projection(w["o"], tensor_cores)
+        self.expand = None
+        hd = dn + self.rot_dim
+        if self.tensor_cores and act_dtype == torch.bfloat16 and self.row % 8 == 0 and hd % 4 == 0 and hd <= 256 and dv <= 256:
+            wk = torch.zeros((H, hd, self.row), dtype=w["uk"].dtype, device=dev)
+            wk[:, :dn, :R] = w["uk"].view(H, dn, R)
+            wk[:, dn:, R:] = torch.eye(self.rot_dim, dtype=w["uk"].dtype, device=dev)
+            wv = torch.zeros((H * dv, self.row), dtype=w["uv"].dtype, device=dev)
+            wv[:, :R] = w["uv"]
+            self.expand = Projection(torch.cat([wk.view(H * hd, self.row), wv], 0).contiguous(), tensor_cores)
 
     def input_weights(self):
         return self._in
@@ -242,14 +257,30 @@ class LatentAttention(Mixer):
         for h in range(H):
             ops.gemm(x[:, h * x_head:h * x_head + K], w[h], out=out[:, h * out_head:h * out_head + N])
 
-    def forward(self, parts, batch, cache):
+    def forward(self, parts, batch, cache, expanded: Optional[bool] = None):
+        """expanded: force (True) or forbid (False) the whole-prompt form; None = whenever the step allows it."""
+        rows, H = parts[0].shape[0], self.heads
+        whole = self.expand is not None and ((batch.all_start and batch.max_new >= 16) if expanded is None else bool(expanded))
         if self.shared_from is None:
             q, dkv, g = parts
+            # the step's rows packed in step order, kept on the (shared) cache view for the layers that read this layer's rows
+            cache.step_rows = torch.empty((rows, self.row), device=q.device, dtype=self.act_dtype) if whole else None
             ops.latent_kv_write(batch, dkv, self.dkv_norm, self.inv_freq, cache.k_pool, rank=self.rank, rot_dim=self.rot_dim,
-                                rot_dims=self.rot_dims, eps=self.eps)
+                                rot_dims=self.rot_dims, eps=self.eps, copy_out=cache.step_rows)
         else:
             q, g = parts
-        rows, H = q.shape[0], self.heads
+            whole = whole and getattr(cache, "step_rows", None) is not None and cache.step_rows.shape[0] == rows
+        if whole:
+            hd = self.dim + self.rot_dim
+            kv = self.expand(cache.step_rows)   # fp32 [rows, H (dim + rot_dim) | H vdim]
+            ops.rope_split(batch, q, self.inv_freq, heads=H, keep=self.dim, rot_dim=self.rot_dim, rot_dims=self.rot_dims, pass_out=None, rot_out=q,
+                           rot_head=hd, rot_col=self.dim)   # in place: each thread reads its pair before it writes it
+            # the buffer as a one-position-per-page pool in step order: position p of sequence s is row cu_tokens[s] + p
+            table = (batch.cu_tokens[:-1, None] + torch.arange(batch.max_new, device=q.device, dtype=torch.int32)[None, :]).contiguous()
+            flat = ops.PackedBatch(batch.cu_tokens, batch.pos0, batch.slot, batch.max_new, table, 1)
+            a = ops.window_attn(flat, q, kv, kv[:, H * hd:], heads=H, kv_heads=H, dim=hd, vdim=self.vdim, scale=self.scale, window=self.window,
+                                keep_first=0, sink=self.sink, gate=g, out_dtype=self.act_dtype, k_row=kv.stride(0), v_row=kv.stride(0))
+            return self.o(a)
         Q = torch.empty((rows, H * self.row), device=q.device, dtype=torch.float32)
         qn = torch.empty((rows, H * self.dim), device=q.device, dtype=self.act_dtype)
         ops.rope_split(batch, q, self.inv_freq, heads=H, keep=self.dim, rot_dim=self.rot_dim, rot_dims=self.rot_dims, pass_out=qn, rot_out=Q,
@@ -295,12 +326,18 @@ class MoEFeedForward:
     run ALL experts as two products over the concatenated experts, the hidden activations multiplied by each token's routing
     weight (0 for the experts it did not choose) in between: the weights are read once, as a decode step would anyway.
     Prompt-sized steps sort the (token, choice) pairs by expert on the device, gather the rows, run each expert's two products
-    on its own rows, and combine per token in choice order (no atomics, so the result does not depend on the batch)."""
+    on its own rows, and combine per token in choice order (no atomics, so the result does not depend on the batch). The sorted
+    form costs two launches per expert and one host read of the experts' row counts, the all-experts form experts / top times
+    the multiply-adds: a step of at least `sorted_min_rows` rows takes the sorted form when its estimated time is the smaller one
+    (`force_sorted` skips the estimate)."""
+
+    TC_RATE, FMA_RATE = 1.0e15, 2.0e13   # multiply-add rates the estimate assumes for bf16 tensor-core and fp32 FMA products (FLOP/s)
+    LAUNCH_COST = 15e-6                   # host time of one product issued from Python (s): what bounds many small launches
 
     def __init__(self, w: Dict[str, torch.Tensor], experts: int, top: int, route_scale: float, act_dtype: torch.dtype, tensor_cores: bool,
-                 act: str = "relu2", shared: bool = False, sorted_min_rows: int = 128):
+                 act: str = "relu2", shared: bool = False, sorted_min_rows: int = 128, force_sorted: bool = False):
         self.experts, self.top, self.route_scale = int(experts), int(top), float(route_scale)
-        self.act_dtype, self.act, self.sorted_min_rows = act_dtype, act, int(sorted_min_rows)
+        self.act_dtype, self.act, self.sorted_min_rows, self.force_sorted = act_dtype, act, int(sorted_min_rows), bool(force_sorted)
         E = self.experts
         self.ff = w["e0.up"].shape[0]
         ups = [w[f"e{e}.up"] for e in range(E)]
@@ -323,11 +360,18 @@ class MoEFeedForward:
             self.up_s = Projection(up_all[E * f:], tensor_cores)
             self.down_s = Projection(down_all[:, E * f:], tensor_cores)
 
+    def _sorted_is_faster(self, rows: int) -> bool:
+        width = self.down_all.out_features
+        rate = self.TC_RATE if self.up_all.tensor_cores and self.act_dtype == torch.bfloat16 else self.FMA_RATE
+        per_choice = 4.0 * rows * self.ff * width / rate   # up + down multiply-adds of one expert-sized slice over all rows
+        moved = 3.0 * rows * self.top * width * 4 / 2.0e12   # gather, per-pair results, combine
+        return self.top * per_choice + 2 * self.experts * self.LAUNCH_COST + moved < self.experts * per_choice
+
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
         """h: the layer input in the activation dtype. Returns fp32 [rows, width]."""
         E, rows = self.experts, h.shape[0]
         z = self.router(h)
-        sorted_form = batch.max_new > 1 and rows >= self.sorted_min_rows
+        sorted_form = batch.max_new > 1 and rows >= self.sorted_min_rows and (self.force_sorted or self._sorted_is_faster(rows))
         idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form)
         sg = z[:, E:E + 1] if self.shared_ff else None
         if not sorted_form:

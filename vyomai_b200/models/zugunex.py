@@ -89,7 +89,7 @@ class ZugunexConfig:
 
 class _Layer:
     def __init__(self, idx: int, spec: dict, w: Dict[str, torch.Tensor], cfg: ZugunexConfig, act_dtype, tensor_cores: bool, kv_dtype,
-                 sorted_min_rows: int):
+                 sorted_min_rows: int, force_sorted: bool):
         p = f"l{idx}."
         sub = lambda pre: {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}  # noqa: E731
         self.eps, self.act_dtype = cfg.eps, act_dtype
@@ -108,7 +108,7 @@ class _Layer:
             else:
                 r = f["router"]
                 self.mlp = MoEFeedForward(sub(p + "mlp."), r["experts"], r["top"], r.get("scale", 1.0), act_dtype, tensor_cores, act="relu2",
-                                          shared=bool(f.get("shared")), sorted_min_rows=sorted_min_rows)
+                                          shared=bool(f.get("shared")), sorted_min_rows=sorted_min_rows, force_sorted=force_sorted)
                 self.moe = True
 
     def cache_specs(self):
@@ -137,7 +137,7 @@ class ZugunexForCausalLM:
 
     def __init__(self, config: ZugunexConfig, weights: Dict[str, torch.Tensor], dtype: torch.dtype = torch.bfloat16,
                  device: Optional[torch.device] = None, tensor_cores: bool = True, kv_dtype: torch.dtype = torch.float32,
-                 sorted_min_rows: int = 128):
+                 sorted_min_rows: int = 128, force_sorted: bool = False):
         if dtype not in (torch.bfloat16, torch.float32):
             raise _lib.VyomError("ZugunexForCausalLM runs in bfloat16 or float32")
         self.config, self.dtype = config, dtype
@@ -153,7 +153,7 @@ class ZugunexForCausalLM:
         self.embed = w["embed"].contiguous()
         self.final_norm = w["final.norm"].contiguous()
         self.head = Projection(w["head"], tensor_cores)
-        self.layers = [_Layer(i, L, w, config, dtype, tensor_cores, kv_dtype, sorted_min_rows) for i, L in enumerate(config.layers)]
+        self.layers = [_Layer(i, L, w, config, dtype, tensor_cores, kv_dtype, sorted_min_rows, force_sorted) for i, L in enumerate(config.layers)]
         self.debug_residuals: Optional[list] = None   # set to [] to collect the residual stream after every layer
 
     @classmethod

@@ -871,9 +871,10 @@ class PackedBatch:
     with attention layers, `block_table` [n, table_width] (int32) over pages of `block_size` positions."""
 
     def __init__(self, cu_tokens: torch.Tensor, pos0: torch.Tensor, slot: torch.Tensor, max_new: int,
-                 block_table: Optional[torch.Tensor] = None, block_size: int = 0):
+                 block_table: Optional[torch.Tensor] = None, block_size: int = 0, all_start: bool = False):
         self.cu_tokens, self.pos0, self.slot, self.max_new = cu_tokens, pos0, slot, int(max_new)
         self.block_table, self.block_size = block_table, int(block_size)
+        self.all_start = bool(all_start)   # host-side knowledge: every sequence of the step starts at position 0 (whole prompts)
         self.n_seqs = pos0.numel()
 
     def _kw(self, pages: bool = False, slots: bool = True) -> dict:
@@ -1009,15 +1010,17 @@ def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_poo
 
 
 def latent_kv_write(batch: PackedBatch, x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, pool: torch.Tensor, *, rank: int, rot_dim: int,
-                    rot_dims: int, eps: float) -> None:
-    """x [rows, rank + rot_dim] -> pool rows [RMS-normed latent * weight | key part rotated by position] at each token's page row."""
-    _need_cuda(x, weight, inv_freq, pool)
+                    rot_dims: int, eps: float, copy_out: Optional[torch.Tensor] = None) -> None:
+    """x [rows, rank + rot_dim] -> pool rows [RMS-normed latent * weight | key part rotated by position] at each token's page row;
+    copy_out [rows, >= rank + rot_dim]: the same rows also packed in step order."""
+    _need_cuda(x, weight, inv_freq, pool, copy_out)
     _rows2d(x, "latent_kv_write x")
     if not pool.is_contiguous() or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2 or weight.numel() != rank:
         raise _lib.VyomError("latent_kv_write: pool contiguous, inv_freq fp32 [rot_dims / 2], weight [rank]")
     _lib.call("vy_latent_kv_write", "VyLatentWrite", x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), rank=rank, rot_dim=rot_dim, rot_dims=rot_dims,
               inv_freq=inv_freq.data_ptr(), weight=weight.data_ptr(), w_dtype=_dt(weight), eps=float(eps), pool=pool.data_ptr(),
-              pool_row=pool.shape[-1] * pool.shape[-2] if pool.dim() == 4 else pool.shape[-1], pool_dtype=_dt(pool), stream=_stream(),
+              pool_row=pool.shape[-1] * pool.shape[-2] if pool.dim() == 4 else pool.shape[-1], pool_dtype=_dt(pool), copy=_ptr(copy_out),
+              ld_copy=copy_out.stride(0) if copy_out is not None else 0, copy_dtype=_dt(copy_out) if copy_out is not None else 0, stream=_stream(),
               **batch._kw(pages=True, slots=False))
 
 

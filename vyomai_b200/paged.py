@@ -200,6 +200,7 @@ class LayerCacheView:
         self.k_pool: torch.Tensor = None
         self.v_pool: torch.Tensor = None
         self.states: Dict[str, torch.Tensor] = {}
+        self.step_rows: torch.Tensor = None   # scratch of the running step (a mixer may leave its packed rows for layers that share its pages)
 
 
 class HybridSequence:
@@ -395,10 +396,11 @@ class HybridBatchEngine:
             at += k
         return offs, at
 
-    def _views(self, flat: torch.Tensor, n: int, width: int, n_ids: int, n_rows: int, max_new: int):
+    def _views(self, flat: torch.Tensor, n: int, width: int, n_ids: int, n_rows: int, max_new: int, all_start: bool = False):
         offs, _ = self._layout(n, width, n_ids, n_rows)
         cu_t, pos_t, slot_t, table_t, ids_t, rows_t = (flat[o:o + k] for o, k in offs)
-        batch = ops.PackedBatch(cu_t, pos_t, slot_t, max_new, table_t.view(n, width) if self.cache.has_pages else None, self.cache.block_size)
+        batch = ops.PackedBatch(cu_t, pos_t, slot_t, max_new, table_t.view(n, width) if self.cache.has_pages else None, self.cache.block_size,
+                                all_start=all_start)
         return batch, ids_t, rows_t
 
     @torch.no_grad()
@@ -469,7 +471,7 @@ class HybridBatchEngine:
             flat = torch.tensor(cu + pos0 + slot + table + ids + rows, dtype=torch.int32)
             if self.device.type == "cuda":   # one pinned staging buffer, one host-to-device copy per step
                 flat = flat.pin_memory().to(self.device, non_blocking=True)
-            batch, ids_t, rows_t = self._views(flat, n, width, len(ids), len(rows), max_new)
+            batch, ids_t, rows_t = self._views(flat, n, width, len(ids), len(rows), max_new, all_start=not any(pos0))
             logits = self.model.step(ids_t, batch, mgr.views, rows_t if rows else None)
         for seq, toks in work:
             seq.num_cached += len(toks)
