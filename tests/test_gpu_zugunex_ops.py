@@ -220,9 +220,9 @@ def test_the_form_is_chosen_by_estimated_time():
         for e in range(32):
             w[f"e{e}.up"], w[f"e{e}.down"] = torch.zeros(ff, width, dtype=dtype, device=DEV), torch.zeros(width, ff, dtype=dtype, device=DEV)
         return MoEFeedForward(w, 32, 4, 1.0, dtype, True)
-    assert not mlp(256, 64, torch.bfloat16)._sorted_is_faster(8192)
+    assert not mlp(1024, 256, torch.bfloat16)._sorted_is_faster(8192)
     assert mlp(2048, 1024, torch.bfloat16)._sorted_is_faster(8192)
-    assert mlp(256, 64, torch.float32)._sorted_is_faster(8192)
+    assert mlp(1024, 256, torch.float32)._sorted_is_faster(8192)
 
 
 def test_sorted_pairs_are_grouped_by_expert_in_row_order():

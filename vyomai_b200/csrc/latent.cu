@@ -179,19 +179,43 @@ struct ScaleDev {
   void* out; long long ld_out; int out_dt;
 };
 
+// one CTA row per token (blockIdx.x), 8 consecutive columns per thread; VEC: 16-byte (bf16) / 32-byte (fp32) accesses
+template <bool VEC>
 __global__ void __launch_bounds__(256) moe_scale_kernel(ScaleDev d) {
   pdl_trigger();
   pdl_wait();
-  const int cols = d.experts * d.ff + d.shared_ff;
-  const long long n = d.rows * cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols;
-    const int c = static_cast<int>(i - r * cols);
-    float w;
-    if (c < d.experts * d.ff) w = d.dense[r * d.experts + c / d.ff];
-    else w = d.sg ? sigmoidf_(d.sg[r * d.ld_sg]) : 1.f;
-    const float v = w == 0.f ? 0.f : ld_as_float(d.h, d.h_dt, r * d.ldh + c) * w;
-    st_from_float(d.out, d.out_dt, r * d.ld_out + c, v);
+  const int cols = d.experts * d.ff + d.shared_ff, ecols = d.experts * d.ff;
+  const long long r = blockIdx.x;
+  const float sgw = d.sg ? sigmoidf_(d.sg[r * d.ld_sg]) : 1.f;
+  const float* dw = d.dense + r * d.experts;
+  for (int c0 = (blockIdx.y * 256 + threadIdx.x) * 8; c0 < cols; c0 += gridDim.y * 256 * 8) {
+    float w[8];
+    bool any = false;
+    if (VEC && d.ff % 8 == 0 && ecols % 8 == 0) {   // the 8 columns belong to one expert (or all to the shared one)
+      const float w0 = c0 < ecols ? dw[c0 / d.ff] : sgw;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = w0;
+      any = w0 != 0.f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = c0 + j;
+        w[j] = c < ecols ? dw[c / d.ff] : sgw;
+        any |= c < cols && w[j] != 0.f;
+      }
+    }
+    float v[8];
+    if (VEC) {
+      if (any) ld8_as_float(d.h, d.h_dt, r * d.ldh + c0, v);   // an unchosen expert's columns are written 0 without being read
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = w[j] == 0.f ? 0.f : v[j] * w[j];
+      st8_from_float(d.out, d.out_dt, r * d.ld_out + c0, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (c0 + j < cols)
+          st_from_float(d.out, d.out_dt, r * d.ld_out + c0 + j, w[j] == 0.f ? 0.f : ld_as_float(d.h, d.h_dt, r * d.ldh + c0 + j) * w[j]);
+    }
   }
 }
 
@@ -371,9 +395,16 @@ extern "C" int vy_moe_scale(const VyMoeScale* p) {
   d.h = p->h; d.ldh = p->ldh; d.h_dt = p->h_dtype;
   d.dense = p->dense; d.sg = p->shared_gate; d.ld_sg = p->ld_gate;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
-  long long blocks = (p->rows * (static_cast<long long>(p->experts) * p->ff + p->shared_ff) + 255) / 256;
-  if (blocks > 16LL * num_sms()) blocks = 16LL * num_sms();
-  VY_CUDA_OK(launch_kernel(moe_scale_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(p->stream), d));
+  const int cols = p->experts * p->ff + p->shared_ff;
+  VY_CHECK_ARG(p->rows <= 2147483647LL, "vy_moe_scale: too many rows");
+  const auto al = [](const void* q, size_t n) { return reinterpret_cast<uintptr_t>(q) % n == 0; };
+  const size_t hb = p->h_dtype == VY_F32 ? 32 : 16, ob = p->out_dtype == VY_F32 ? 32 : 16;
+  const bool vec = cols % 8 == 0 && p->ldh % 8 == 0 && p->ld_out % 8 == 0 && al(p->h, hb) && al(p->out, ob);
+  int gy = (cols + 256 * 8 - 1) / (256 * 8);
+  if (gy > 64) gy = 64;
+  const dim3 grid(static_cast<unsigned>(p->rows), gy);
+  VY_CUDA_OK(vec ? launch_kernel(moe_scale_kernel<true>, grid, dim3(256), 0, static_cast<cudaStream_t>(p->stream), d)
+                 : launch_kernel(moe_scale_kernel<false>, grid, dim3(256), 0, static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;

@@ -375,8 +375,12 @@ class MoEFeedForward:
         idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form)
         sg = z[:, E:E + 1] if self.shared_ff else None
         if not sorted_form:
-            u = self.up_all(h, act=self.act, out_dtype=torch.float32)
-            us = ops.moe_scale(u, dense, experts=E, ff=self.ff, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype)
+            # few rows: fp32 hidden activations, weighted, rounded once. Prompt-sized steps write them in the activation dtype from
+            # the product's epilogue and weight them in place (half the bytes of the step's largest tensor, one more rounding)
+            wide = rows > 32 and self.act_dtype != torch.float32
+            u = self.up_all(h, act=self.act, out_dtype=self.act_dtype if wide else torch.float32)
+            us = ops.moe_scale(u, dense, experts=E, ff=self.ff, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype,
+                               out=u if wide else None)
             return self.down_all(us)
         counts, offsets, perm, inv = ops.moe_sort(idx, E)
         xg = ops.moe_gather(h, perm, self.top, self.act_dtype)

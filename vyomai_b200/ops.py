@@ -1055,12 +1055,13 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, dense:
 
 
 def moe_scale(h: torch.Tensor, dense: Optional[torch.Tensor], *, experts: int, ff: int, shared_ff: int, shared_gate: Optional[torch.Tensor],
-              out_dtype: torch.dtype) -> torch.Tensor:
+              out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """h [rows, experts * ff + shared_ff] times each column's routing weight (dense [rows, experts]; the shared columns times
-    sigmoid(shared_gate[row, 0]))."""
-    _need_cuda(h, dense, shared_gate)
+    sigmoid(shared_gate[row, 0])). out may be h itself (each element is read and written by one thread)."""
+    _need_cuda(h, dense, shared_gate, out)
     _rows2d(h, "moe_scale h")
-    out = torch.empty(h.shape, device=h.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty(h.shape, device=h.device, dtype=out_dtype)
     _lib.call("vy_moe_scale", "VyMoeScale", rows=h.shape[0], experts=experts, ff=ff, shared_ff=shared_ff, h=h.data_ptr(), ldh=h.stride(0),
               h_dtype=_dt(h), dense=_ptr(dense), shared_gate=_ptr(shared_gate), ld_gate=shared_gate.stride(0) if shared_gate is not None else 0,
               out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
