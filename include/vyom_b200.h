@@ -666,6 +666,9 @@ typedef struct VyRmsNorm {
   float eps, coef;
   int32_t accumulate;
   void* out; int64_t ld_out; int32_t out_dtype;
+  /* optional second copy of what was stored in out, in another dtype: copy[token * ld_copy + group * width + c] (the bf16
+   * input of the next product beside an fp32 residual that was just accumulated into) */
+  void* copy; int64_t ld_copy; int32_t copy_dtype;
   void* stream;
 } VyRmsNorm;
 VY_API int vy_rms_norm(const VyRmsNorm* p);

@@ -19,6 +19,7 @@ struct NormDev {
   const void* gate; long long ld_gate; int gate_dt, gate_act;
   float eps, coef; int accumulate;
   void* out; long long ld_out; int out_dt;
+  void* copy; long long ld_copy; int copy_dt;
 };
 
 __global__ void __launch_bounds__(128) rms_norm_kernel(NormDev d) {
@@ -50,6 +51,7 @@ __global__ void __launch_bounds__(128) rms_norm_kernel(NormDev d) {
     }
     if (d.accumulate) y += ld_as_float(d.out, d.out_dt, oo + c);
     st_from_float(d.out, d.out_dt, oo + c, y);
+    if (d.copy) st_from_float(d.copy, d.copy_dt, tok * d.ld_copy + static_cast<long long>(grp) * d.width + c, y);
   }
 }
 
@@ -129,6 +131,11 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
           y[0] += o.x; y[1] += o.y; y[2] += o.z; y[3] += o.w;
         }
         *op = make_float4(y[0], y[1], y[2], y[3]);
+        if (d.copy) {
+          const long long co = static_cast<long long>(tok) * d.ld_copy + static_cast<long long>(grp) * d.width + c;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) st_from_float(d.copy, d.copy_dt, co + e, y[e]);
+        }
       } else {
         const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
         uint2 pk;
@@ -154,6 +161,7 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
       }
       if (d.accumulate) y += ld_as_float(d.out, d.out_dt, oo + c);
       st_from_float(d.out, d.out_dt, oo + c, y);
+      if (d.copy) st_from_float(d.copy, d.copy_dt, static_cast<long long>(tok) * d.ld_copy + static_cast<long long>(grp) * d.width + c, y);
     }
   }
 }
@@ -799,6 +807,8 @@ extern "C" int vy_rms_norm(const VyRmsNorm* p) {
   d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype; d.gate_act = p->gate_act;
   d.eps = p->eps; d.coef = p->coef == 0.f ? 1.f : p->coef; d.accumulate = p->accumulate;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
+  VY_CHECK_ARG(!p->copy || (dtype_ok(p->copy_dtype) && p->out_dtype == VY_F32), "vy_rms_norm: the second copy goes with an fp32 out");
+  d.copy = p->copy; d.ld_copy = p->ld_copy; d.copy_dt = p->copy_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(p->stream);
   const int tpr = d.width <= 256 ? 32 : d.width <= 1024 ? 128 : d.width <= 2048 ? 256 : 0;
   const long long blocks = tpr ? (d.rows + 256 / tpr - 1) / (256 / tpr) : (d.rows + 3) / 4;

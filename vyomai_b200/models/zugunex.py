@@ -114,18 +114,24 @@ class _Layer:
     def cache_specs(self):
         return [self.mixer.cache_spec()]
 
-    def _act(self, x: torch.Tensor) -> torch.Tensor:
-        """The sublayers read the fp32 residual itself; the tensor-core products take its bf16 rounding."""
-        return x if self.act_dtype == torch.float32 else ops.unary(x, None, self.act_dtype)
+    def _round(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """Room for the bf16 rounding of the residual that the next tensor-core product reads (None for fp32 models: they read x)."""
+        return None if self.act_dtype == torch.float32 else torch.empty(x.shape, device=x.device, dtype=self.act_dtype)
 
-    def forward(self, x: torch.Tensor, batch: ops.PackedBatch, caches) -> None:
-        P = self.inp(self._act(x))
+    def forward(self, x: torch.Tensor, h: Optional[torch.Tensor], batch: ops.PackedBatch, caches, last: bool = False) -> Optional[torch.Tensor]:
+        """x: the fp32 residual (updated in place); h: its rounding in the activation dtype (None: x itself is read). Every sublayer
+        reads the residual itself; the norm that adds a sublayer's output into x also writes the rounding the next product reads.
+        Returns the rounding of the layer's result (None for fp32 models and for the last layer, whose reader is the final norm)."""
+        P = self.inp(x if h is None else h)
         y = self.mixer.forward([P[:, o:o + n] for o, n in self.spans], batch, caches[0])
-        ops.rms_norm(y, self.norm1, eps=self.eps, w_mode="plain", accumulate=True, out=x)
+        h = None if last and self.mlp is None else self._round(x)
+        ops.rms_norm(y, self.norm1, eps=self.eps, w_mode="plain", accumulate=True, out=x, copy_out=h)
         if self.mlp is not None:
-            h = self._act(x)
-            y = self.mlp.forward(h, batch) if self.moe else self.mlp.forward(h)
-            ops.rms_norm(y, self.norm2, eps=self.eps, w_mode="plain", accumulate=True, out=x)
+            hin = x if h is None else h
+            y = self.mlp.forward(hin, batch) if self.moe else self.mlp.forward(hin)
+            h = None if last else self._round(x)
+            ops.rms_norm(y, self.norm2, eps=self.eps, w_mode="plain", accumulate=True, out=x, copy_out=h)
+        return h
 
 
 class ZugunexForCausalLM:
@@ -189,8 +195,9 @@ class ZugunexForCausalLM:
     def step(self, ids: torch.Tensor, batch: ops.PackedBatch, caches, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         cfg = self.config
         x = ops.embed_rows(ids, self.embed, 1.0, torch.float32)
-        for L, c in zip(self.layers, caches):
-            L.forward(x, batch, c)
+        h = None if self.dtype == torch.float32 else ops.unary(x, None, self.dtype)
+        for i, (L, c) in enumerate(zip(self.layers, caches)):
+            h = L.forward(x, h, batch, c, last=i == len(self.layers) - 1)
             if self.debug_residuals is not None:
                 self.debug_residuals.append(x.clone())
         if want_rows is None or want_rows.numel() == 0:

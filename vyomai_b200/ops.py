@@ -930,11 +930,12 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tenso
 
 def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_mode: Optional[str] = "plain", groups: int = 1,
              gate: Optional[torch.Tensor] = None, gate_act: Optional[str] = "sigmoid", coef: float = 1.0, accumulate: bool = False,
-             row_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+             row_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+             copy_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Grouped RMS norm (fp32 statistics): each row of x is `groups` runs of width x.shape[1] / groups, every run normalised on
     its own, times the weight (plain or 1 + w, shared by the runs), times an optional (sigmoid) gate, times coef; optionally
-    added into `out`, optionally reading rows x[row_index]."""
-    _need_cuda(x, weight, gate, out, row_index)
+    added into `out`, optionally reading rows x[row_index]. copy_out: a second copy of what `out` (fp32) receives, in its own dtype."""
+    _need_cuda(x, weight, gate, out, row_index, copy_out)
     _rows2d(x, "rms_norm x")
     tokens = x.shape[0] if row_index is None else row_index.numel()
     if x.shape[1] % groups:
@@ -955,7 +956,8 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_m
               ldx=x.stride(0), x_dtype=_dt(x), weight=_ptr(weight), w_dtype=_dt(weight) if weight is not None else 0,
               w_mode=W_MODE[w_mode], gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0,
               gate_dtype=_dt(gate) if gate is not None else 0, gate_act=UACT[gate_act], eps=float(eps), coef=float(coef),
-              accumulate=1 if accumulate else 0, out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+              accumulate=1 if accumulate else 0, out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), copy=_ptr(copy_out),
+              ld_copy=copy_out.stride(0) if copy_out is not None else 0, copy_dtype=_dt(copy_out) if copy_out is not None else 0, stream=_stream())
     return out
 
 
