@@ -699,8 +699,9 @@ VY_API int vy_kv_page_write(const VyKvWrite* p);
  * rows of the cache; positions do not enter the score otherwise. score = (q . k) * scale. With `sink` (one number per
  * query head) the softmax denominator also holds exp(sink[h]): it has no key and no value. With `gate` the head's
  * output is multiplied by sigmoid(gate[token, h]). Query head h reads kv head h / (heads / kv_heads). The step's own
- * keys must already be in the pools (vy_kv_page_write). One warp per query when a sequence brings several tokens; the
- * four warps of a CTA split the keys of a single-token query (decode). */
+ * keys must already be in the pools (vy_kv_page_write). One warp per query when a sequence brings a few tokens, 64 x 64
+ * register tiles for prompts; the warps of a CTA split the keys of a single-token query (decode), or, when 8 or more query
+ * heads share a key / value head, the heads of the token are the rows of a 16 x 64 tile. */
 typedef struct VyWinAttn {
   int32_t n_seqs, max_new;
   const int32_t* cu_tokens; const int32_t* pos0;
@@ -716,8 +717,12 @@ typedef struct VyWinAttn {
   /* row strides of the two pools in elements; 0 = kv_heads * dim and kv_heads * vdim. With explicit strides k_pool and v_pool
    * may be views of ONE pool (latent attention: the value is the leading part of the key row). */
   int64_t k_row, v_row;
+  /* optional scratch of vy_window_attn_workspace_floats(n_seqs, heads, vdim) floats: single-token steps whose query heads share
+   * key / value rows in groups of 8 or more split a sequence's keys over several CTAs and combine the parts from here */
+  float* workspace; int64_t workspace_floats;
   void* stream;
 } VyWinAttn;
+VY_API int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t vdim);
 VY_API int vy_window_attn(const VyWinAttn* p);
 
 /* Depthwise causal convolution over time with carried taps, then an activation:

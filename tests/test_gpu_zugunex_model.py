@@ -165,10 +165,10 @@ def test_first_tokens_of_a_sequence():
         assert HU.rel_err(HU.feed_in_portions(eng, "s", toks, cuts), ref) < TOL[torch.float32], cuts
 
 
-@pytest.mark.parametrize("dtype,cfg_name", [(torch.float32, "small"), (torch.bfloat16, "aligned")])
+@pytest.mark.parametrize("dtype,cfg_name", [(torch.float32, "small"), (torch.bfloat16, "aligned"), (torch.float32, "many_heads")])
 def test_long_decoding_through_the_captured_step(dtype, cfg_name):
     """150 single-token steps (several windows, many page borders); from the third step of a shape on they replay a CUDA graph."""
-    cfg = U.small_config() if cfg_name == "small" else U.aligned_config()
+    cfg = {"small": U.small_config, "aligned": U.aligned_config, "many_heads": U.many_heads_config}[cfg_name]()
     model, W = U.build(cfg, dtype=dtype)
     eng, _ = HU.engine_for(model, block_size=8, use_graph=True)
     toks = HU.tokens(160, cfg["vocab"], 14)

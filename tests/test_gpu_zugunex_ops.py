@@ -286,3 +286,36 @@ def test_single_token_attention_with_heads_grouped_per_cta(dim, vdim, kv_heads):
         sub = ops.PackedBatch(t(list(range(9))), t(pos0[a:a + 8]), t([0] * 8), 1, batch.block_table[a:a + 8].contiguous(), bs)
         part = ops.window_attn(sub, q[a:a + 8], kp, vp, gate=gate[a:a + 8], **kw)
         assert float((part - whole[a:a + 8]).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("alias", [True, False])
+@pytest.mark.parametrize("heads,dim,vdim,window", [(24, 40, 24, 300), (8, 22, 10, 0), (16, 224, 192, 130), (32, 64, 64, 64)])
+def test_single_token_attention_with_heads_as_tile_rows(heads, dim, vdim, window, alias):
+    """Eight or more query heads on one key / value head: the token's heads are the rows of a tile, a sequence's keys are split over
+    CTAs and merged. Against a float64 softmax over the gathered pool rows: split edges, a partly filled head tile, the sink in
+    one split only, values as the leading channels of the key rows (one pool) or in a pool of their own."""
+    from vyomai_b200 import ops
+    bs = 16
+    g = torch.Generator().manual_seed(heads + dim)
+    pos0 = [0, 63, 64, 700, 257]
+    n = len(pos0)
+    batch, table, _, n_blocks, _ = HU.shuffled_batch([1] * n, pos0, bs, DEV)
+    kp = torch.randn(n_blocks, bs, 1, dim, generator=g)
+    vp = kp[..., :vdim] if alias else torch.randn(n_blocks, bs, 1, vdim, generator=g)
+    q = torch.randn(n, heads * dim, generator=g)
+    sink, gate = torch.randn(heads, generator=g), torch.randn(n, heads, generator=g)
+    kd = kp.to(DEV)
+    vd = kd if alias else vp.to(DEV)
+    got = ops.window_attn(batch, q.to(DEV), kd, vd, heads=heads, kv_heads=1, dim=dim, vdim=vdim, scale=0.2, window=window, keep_first=0,
+                          sink=sink.to(DEV), gate=gate.to(DEV), k_row=dim, v_row=dim if alias else vdim).cpu().double()
+    for s, p in enumerate(pos0):
+        lo = 0 if window <= 0 else max(0, p - window + 1)
+        rows = [(table[s][j // bs], j % bs) for j in range(lo, p + 1)]
+        K = torch.stack([kp[b, o, 0] for b, o in rows]).double()
+        V = torch.stack([vp[b, o, 0] for b, o in rows]).double()
+        for h in range(heads):
+            sc = K @ q[s, h * dim:(h + 1) * dim].double() * 0.2
+            mx = torch.maximum(sc.max(), sink[h].double())
+            e = torch.exp(sc - mx)
+            o = (e[:, None] * V).sum(0) / (e.sum() + torch.exp(sink[h].double() - mx)) * torch.sigmoid(gate[s, h].double())
+            assert float((got[s, h * vdim:(h + 1) * vdim] - o).abs().max()) < 1e-5, (s, h)

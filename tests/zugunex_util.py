@@ -56,6 +56,13 @@ def aligned_config(width=128, window=24) -> dict:
     ], width=width, vocab=203)
 
 
+def many_heads_config() -> dict:
+    """8 and 16 query heads over one latent row: single tokens take the heads-as-rows attention with the keys split over CTAs."""
+    a = dict(dim=8, rot_dim=4, vdim=12, rank=20, window=70, scale=0.3, base=50.0)
+    return config([layer(attn(heads=8, **a), dense(ff=48)), layer(attn(heads=16, **a, kv_from=0), moe(experts=4, top=2, ff=16, shared_ff=16))],
+                  width=48, vocab=101)
+
+
 def f64(weights: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     return {k: v.double() for k, v in weights.items()}
 

@@ -850,6 +850,10 @@ extern "C" int vy_kv_page_write(const VyKvWrite* p) {
   return VY_OK;
 }
 
+extern "C" int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t vdim) {
+  return vy::window_attn_heads_workspace_floats(n_seqs, heads, vdim);
+}
+
 extern "C" int vy_window_attn(const VyWinAttn* p) {
   using namespace vy;
   VY_CHECK_ARG(p != nullptr, "vy_window_attn: null params");
@@ -881,6 +885,12 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
   VY_CHECK_ARG(p->dim <= 32 * WA_VR, "vy_window_attn: dim %d > %d", p->dim, 32 * WA_VR);
   if (p->max_new >= WA_TILED_MIN) {   // prompt-sized: 64 x 64 register-tiled form
     VY_CUDA_OK(launch_window_attn_tiled(d, p->n_seqs, p->max_new, st));
+  } else if (p->max_new == 1 && window_attn_heads_applies(d)) {
+    int launches = 1;
+    VY_CUDA_OK(launch_window_attn_heads(d, p->n_seqs, p->workspace, p->workspace_floats, st, &launches));
+    VY_LAUNCH_OK();
+    count_launch(launches);
+    return VY_OK;
   } else if (p->max_new == 1) {
     const auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
     const bool vec = p->pool_dtype == VY_F32 && p->dim % 4 == 0 && p->vdim % 4 == 0 && d.k_row % 4 == 0 && d.v_row % 4 == 0 && al(p->k_pool) && al(p->v_pool);

@@ -463,6 +463,235 @@ __global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kern
   }
 }
 
+// ---- single tokens, many query heads per key / value head ---------------------------------------------------------------------
+// Latent rows (one key / value head for all query heads) and wide head groups: the heads of ONE token are the query rows of a tile.
+// A CTA owns (sequence, 16 heads of one key / value head, one split of the visible keys) and walks its keys 64 at a time: the key
+// tile goes to shared memory once (the value tile too, unless values are the leading channels of the key rows), thread (key, 4
+// heads) contracts a key row with 4 query rows (no per-pair warp reduction: a lane owns a key), two heads per warp update the
+// online softmax, thread (4 heads, every 64th channel) accumulates the output. With several splits the partial (max, sum, output)
+// of each goes to a workspace and window_attn_heads_merge_kernel combines them; the sink enters split 0.
+constexpr int WH_H = 16, WH_K = 64, WH_T = 256, WH_VC = 4;   // heads and keys per tile, threads, value channels per thread (vdim <= 256)
+
+__global__ void __launch_bounds__(WH_T) window_attn_heads_kernel(WinDev d, int ldk, int ldv, int dim4, int vdim4, bool qvec, bool kvvec, bool alias,
+                                                                 int splits, float* ws) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float wh_smem[];
+  constexpr int LDS_ = WH_K + 4;
+  float* Qs = wh_smem;                       // [WH_H][ldk]
+  float* Ks = Qs + WH_H * ldk;               // [WH_K][ldk]
+  float* Vs = alias ? Ks : Ks + WH_K * ldk;  // [WH_K][ldv] (alias: the key rows themselves, ldv == ldk)
+  float* Ss = (alias ? Ks + WH_K * ldk : Vs + WH_K * ldv);   // [WH_H][LDS_] scores, then weights
+  float* corr_s = Ss + WH_H * LDS_;          // [WH_H]
+  float* m_s = corr_s + WH_H;                // [WH_H]
+  float* l_s = m_s + WH_H;                   // [WH_H]
+  int* krow_s = reinterpret_cast<int*>(l_s + WH_H);   // [WH_K] pool row of each key of the tile, -1 past the end
+  const int per_kv = d.heads / d.kv_heads, tiles = (per_kv + WH_H - 1) / WH_H;
+  const int s = blockIdx.z, g = blockIdx.y / tiles, h0 = g * per_kv + (blockIdx.y % tiles) * WH_H, split = blockIdx.x;
+  const int nh = min(WH_H, g * per_kv + per_kv - h0);
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int base = d.cu[s];
+  if (d.cu[s + 1] - base <= 0) return;
+  const long long qrow = base;
+  rows_to_smem<WH_T>(Qs, ldk, WH_H, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE,
+               [&](int i) { return i < nh ? qrow * d.ldq + static_cast<long long>(h0 + i) * d.dim : -1LL; });
+  const int pos = d.pos0[s];
+  const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
+  const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
+  const int count = nA + (pos + 1 - lowB);
+  // this split's keys: tiles of WH_K dealt out in contiguous runs
+  const int ktiles = (count + WH_K - 1) / WH_K, tper = (ktiles + splits - 1) / splits;
+  const int c_begin = min(split * tper * WH_K, count), c_end = min((split + 1) * tper * WH_K, count);
+  const int* tab = d.table + static_cast<long long>(s) * d.tw;
+  // softmax statistics of heads 2 warp, 2 warp + 1 (lane-uniform)
+  float m[2], l[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int hh = 2 * warp + e;
+    const bool sk = d.sink && split == 0 && hh < nh;
+    m[e] = sk ? ld_as_float(d.sink, d.sink_dt, h0 + hh) : -INFINITY;
+    l[e] = sk ? 1.f : 0.f;
+  }
+  const int kj = t & 63, hq = t >> 6;   // score phase: key kj, heads 4 hq .. 4 hq + 3; output phase: channels kj + 64 cc, same heads
+  float acc[4][WH_VC];
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+#pragma unroll
+    for (int cc = 0; cc < WH_VC; ++cc) acc[e][cc] = 0.f;
+  for (int c0 = c_begin; c0 < c_end; c0 += WH_K) {
+    __syncthreads();   // the previous tile's readers are done (first pass: Qs is complete after the barrier below)
+    if (t < WH_K) {
+      const int c = c0 + t;
+      int row = -1;
+      if (c < c_end) {
+        const int kp = c < nA ? c : lowB + (c - nA);
+        row = tab[kp / d.bs] * d.bs + kp % d.bs;
+      }
+      krow_s[t] = row;
+    }
+    __syncthreads();
+    rows_to_smem<WH_T>(Ks, ldk, WH_K, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE,
+                 [&](int j) { return krow_s[j] >= 0 ? static_cast<long long>(krow_s[j]) * d.k_row + static_cast<long long>(g) * d.dim : -1LL; });
+    if (!alias)
+      rows_to_smem<WH_T>(Vs, ldv, WH_K, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE,
+                   [&](int j) { return krow_s[j] >= 0 ? static_cast<long long>(krow_s[j]) * d.v_row + static_cast<long long>(g) * d.vdim : -1LL; });
+    __syncthreads();
+    {
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* kr = Ks + kj * ldk;
+      const float* q0 = Qs + (4 * hq) * ldk;
+#pragma unroll 2
+      for (int c = 0; c < dim4; c += 4) {
+        const float4 k4 = f4(kr + c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[e] = dot4(f4(q0 + e * ldk + c), k4, sc[e]);
+      }
+      const bool vis = krow_s[kj] >= 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) Ss[(4 * hq + e) * LDS_ + kj] = vis ? sc[e] * d.scale : -INFINITY;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float* pr = Ss + (2 * warp + e) * LDS_;
+      const float a = pr[lane], b = pr[lane + 32];
+      const float mn = fmaxf(m[e], warp_max(fmaxf(a, b)));
+      const float cr = mn == -INFINITY ? 1.f : expf(m[e] - mn);
+      const float pa = a == -INFINITY ? 0.f : expf(a - mn), pb = b == -INFINITY ? 0.f : expf(b - mn);
+      pr[lane] = pa;
+      pr[lane + 32] = pb;
+      l[e] = fmaf(l[e], cr, warp_sum(pa + pb));
+      m[e] = mn;
+      if (lane == 0) corr_s[2 * warp + e] = cr;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float cr = corr_s[4 * hq + e];
+#pragma unroll
+      for (int cc = 0; cc < WH_VC; ++cc) acc[e][cc] *= cr;
+    }
+    const int nk = min(WH_K, (c_end - c0 + 3) & ~3);
+    for (int j4 = 0; j4 < nk; j4 += 4) {
+      float4 p4[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) p4[e] = f4(Ss + (4 * hq + e) * LDS_ + j4);
+#pragma unroll
+      for (int cc = 0; cc < WH_VC; ++cc) {
+        const int col = kj + 64 * cc;
+        if (col < vdim4) {
+          const float v0 = Vs[(j4 + 0) * ldv + col], v1 = Vs[(j4 + 1) * ldv + col], v2 = Vs[(j4 + 2) * ldv + col], v3 = Vs[(j4 + 3) * ldv + col];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float a = acc[e][cc];
+            a = fmaf(p4[e].x, v0, a);
+            a = fmaf(p4[e].y, v1, a);
+            a = fmaf(p4[e].z, v2, a);
+            a = fmaf(p4[e].w, v3, a);
+            acc[e][cc] = a;
+          }
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) { m_s[2 * warp + e] = m[e]; l_s[2 * warp + e] = l[e]; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int hh = 4 * hq + e;
+    if (hh >= nh) continue;
+    const int h = h0 + hh;
+    if (splits == 1) {
+      float og = 1.f / l_s[hh];
+      if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
+#pragma unroll
+      for (int cc = 0; cc < WH_VC; ++cc) {
+        const int col = kj + 64 * cc;
+        if (col < d.vdim) st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, acc[e][cc] * og);
+      }
+    } else {
+      float* wp = ws + ((static_cast<long long>(s) * d.heads + h) * splits + split) * (d.vdim + 2);
+      if (kj == 0) { wp[0] = m_s[hh]; wp[1] = l_s[hh]; }
+#pragma unroll
+      for (int cc = 0; cc < WH_VC; ++cc) {
+        const int col = kj + 64 * cc;
+        if (col < d.vdim) wp[2 + col] = acc[e][cc];
+      }
+    }
+  }
+}
+
+// combines the splits of one (sequence, head): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), times the output gate
+__global__ void __launch_bounds__(64) window_attn_heads_merge_kernel(WinDev d, int splits, const float* ws) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.y, h = blockIdx.x;
+  const int base = d.cu[s];
+  if (d.cu[s + 1] - base <= 0) return;
+  const float* wp = ws + (static_cast<long long>(s) * d.heads + h) * splits * (d.vdim + 2);
+  float M = -INFINITY;
+  for (int k = 0; k < splits; ++k) M = fmaxf(M, wp[k * (d.vdim + 2)]);
+  float L = 0.f;
+  for (int k = 0; k < splits; ++k) {
+    const float mk = wp[k * (d.vdim + 2)];
+    if (mk != -INFINITY) L = fmaf(wp[k * (d.vdim + 2) + 1], expf(mk - M), L);
+  }
+  float og = 1.f / L;
+  const long long qrow = base;
+  if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
+  for (int c = threadIdx.x; c < d.vdim; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < splits; ++k) {
+      const float mk = wp[k * (d.vdim + 2)];
+      if (mk != -INFINITY) a = fmaf(wp[k * (d.vdim + 2) + 2 + c], expf(mk - M), a);
+    }
+    st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + c, a * og);
+  }
+}
+
+// heads per key / value head from which the heads-as-rows form is used for single tokens
+constexpr int WH_MIN_HEADS = 8;
+
+bool window_attn_heads_applies(const WinDev& d) { return d.heads / d.kv_heads >= WH_MIN_HEADS && d.dim <= 256 && d.vdim <= 64 * WH_VC; }
+
+long long window_attn_heads_workspace_floats(int n_seqs, int heads, int vdim) { return static_cast<long long>(n_seqs) * heads * 16 * (vdim + 2); }
+
+cudaError_t launch_window_attn_heads(const WinDev& d, int n_seqs, float* ws, long long ws_floats, cudaStream_t st, int* launches) {
+  const int dim4 = (d.dim + 3) & ~3, vdim4 = (d.vdim + 3) & ~3;
+  const bool alias = d.vp == d.kp && d.v_row == d.k_row && d.kv_heads == 1 && d.vdim <= d.dim;   // values = leading channels of the key rows
+  const int ldk = ((dim4 >> 2) & 1) ? dim4 + 8 : dim4 + 4;   // (row stride / 4) odd: 16-byte reads of rows 1 apart do not collide
+  const int ldv = alias ? ldk : vdim4 + 4;                    // rows are filled 16 bytes at a time: a multiple of 4; reads are scalar, consecutive channels
+  const size_t floats = static_cast<size_t>(WH_H + WH_K) * ldk + (alias ? 0 : static_cast<size_t>(WH_K) * ldv) + WH_H * (WH_K + 4) + 3 * WH_H;
+  const size_t smem = sizeof(float) * floats + sizeof(int) * WH_K;
+  const auto al = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool qvec = d.q_dt == VY_F32 && d.dim % 4 == 0 && d.ldq % 4 == 0 && al(d.q);
+  const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && d.k_row % 4 == 0 && d.v_row % 4 == 0 && al(d.kp) && al(d.vp);
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(window_attn_heads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    allowed = smem;
+  }
+  const int per_kv = d.heads / d.kv_heads, tiles = (per_kv + WH_H - 1) / WH_H;
+  // splits: enough CTAs for two per SM, at most one per 64 keys of the longest possible context, at most 16 and what the workspace holds
+  const long long ctas = static_cast<long long>(n_seqs) * d.kv_heads * tiles;
+  const long long kmax = d.window > 0 ? static_cast<long long>(d.window) + d.keep : static_cast<long long>(d.tw) * d.bs;
+  long long splits = (2LL * num_sms() + ctas - 1) / ctas;
+  splits = splits < (kmax + WH_K - 1) / WH_K ? splits : (kmax + WH_K - 1) / WH_K;
+  if (splits > 16) splits = 16;
+  if (!ws || ws_floats < static_cast<long long>(n_seqs) * d.heads * splits * (d.vdim + 2)) splits = 1;
+  if (splits < 1) splits = 1;
+  cudaError_t e = launch_kernel(window_attn_heads_kernel, dim3(static_cast<unsigned>(splits), d.kv_heads * tiles, n_seqs), dim3(WH_T), smem, st, d, ldk,
+                                ldv, dim4, vdim4, qvec, kvvec, alias, static_cast<int>(splits), ws);
+  *launches = 1;
+  if (e != cudaSuccess || splits == 1) return e;
+  *launches = 2;
+  return launch_kernel(window_attn_heads_merge_kernel, dim3(d.heads, n_seqs), dim3(64), 0, st, d, static_cast<int>(splits), static_cast<const float*>(ws));
+}
+
 template <int MV, int BN>
 static cudaError_t launch_wt(const WinDev& d, int n_seqs, int max_new, cudaStream_t st) {
   constexpr int WT_N = BN, WT_LDP = BN + 4;

@@ -1002,7 +1002,10 @@ def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_poo
     _need_cuda(q, k_pool, v_pool, sink, gate)
     _rows2d(q, "window_attn q")
     out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or q.dtype)
-    _lib.call("vy_window_attn", "VyWinAttn", q=q.data_ptr(), ldq=q.stride(0), q_dtype=_dt(q), k_pool=k_pool.data_ptr(),
+    ws = None
+    if batch.max_new == 1 and heads // kv_heads >= 8:   # the heads-as-rows form splits keys over CTAs and merges from a scratch buffer
+        ws = torch.empty(int(_lib.lib().vy_window_attn_workspace_floats(batch.n_seqs, heads, vdim)), device=q.device, dtype=torch.float32)
+    _lib.call("vy_window_attn", "VyWinAttn", workspace=_ptr(ws), workspace_floats=ws.numel() if ws is not None else 0, q=q.data_ptr(), ldq=q.stride(0), q_dtype=_dt(q), k_pool=k_pool.data_ptr(),
               v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale),
               window=int(window), keep_first=int(keep_first), sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
               gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0, gate_dtype=_dt(gate) if gate is not None else 0,
