@@ -1083,7 +1083,7 @@ def run_hybrid(args):
 # --workload latent: the Zugunex latent-attention / mixture-of-experts decoder beside the Gelutar hybrid decoder at equal
 # width / depth / vocabulary (both run on HybridBatchEngine's packed step)
 # ------------------------------------------------------------------------------------------------
-LATENT_KERNELS = ("window_attn_tiled", "window_attn_decode", "window_attn", "latent_kv_write", "rope_split", "moe_route", "moe_scale", "moe_sort",
+LATENT_KERNELS = ("window_attn_tiled", "window_attn_decode", "window_attn_heads_merge", "window_attn_heads", "window_attn", "latent_kv_write", "rope_split", "moe_route", "moe_scale", "moe_sort",
                   "moe_gather", "moe_combine", "linear_tile", "linear_rows", "linear_attn_chunk", "linear_attn", "delta_rule", "delta_prep",
                   "causal_conv", "rms_norm", "kv_page_write", "unary", "embed_rows", "gemm_skinny", "gemm_kernel", "argmax")
 
@@ -1181,7 +1181,8 @@ def measure_latent(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, de
     if ms:
         z["window_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
     # single-token attention: the bytes of the visible latent rows, read once per (sequence, layer) if the heads share them through L2
-    ms = z["decode_kernels_eager"].get("window_attn_decode", {}).get("ms")
+    dk = z["decode_kernels_eager"]   # 8 or more heads per latent row: the heads-as-rows kernel and its merge; else the key-parallel kernel
+    ms = sum(dk.get(k, {}).get("ms", 0.0) for k in ("window_attn_heads", "window_attn_heads_merge", "window_attn_decode"))
     if ms:
         by = len(cfgd["layers"]) * batch_decode * min(W, prompt) * row * 4
         dfl = len(cfgd["layers"]) * batch_decode * m["heads"] * min(W, prompt) * (row + m["kv_rank"]) * 2
