@@ -75,3 +75,32 @@ def build(cfg_dict: dict, dtype=torch.float32, seed=0, weights=None, **kw):
     kw.setdefault("sorted_min_rows", 8)   # both forms of the experts' sum come up at test sizes
     kw.setdefault("force_sorted", True)
     return ZugunexForCausalLM(cfg, w, dtype=dtype, device="cuda", **kw), f64(w)
+
+
+def random_config(seed: int, experts: bool = True) -> dict:
+    """A configuration drawn from the design's whole space: 3-6 layers in any order of owners and sharers, head counts from 1 to 12,
+    unrelated channel counts, windows shorter and longer than the test sequences, every feed-forward kind (experts=False: the same
+    draw with every mixture replaced by a dense feed-forward)."""
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(0, len(xs), (1,), generator=g))]  # noqa: E731
+    width = pick([48, 64, 96, 160])
+    layers, owners = [], []
+    for i in range(pick([3, 4, 5, 6])):
+        own = not owners or pick([True, False])
+        if own:
+            geo = dict(rank=pick([12, 16, 40, 64, 96]), rot_dim=pick([2, 4, 8, 16, 32]), base=pick([10.0, 1000.0, 250000.0]))
+            owners.append((i, geo))
+            src = None
+        else:
+            src, geo = pick(owners)
+        m = attn(heads=pick([1, 2, 3, 4, 6, 8, 12]), dim=pick([4, 8, 16, 24, 32]), vdim=pick([4, 8, 20, 32, 48]), window=pick([1, 3, 17, 50, 200]),
+                 scale=pick([0.1, 0.25, 0.5]), kv_from=src, **geo)
+        kind = pick(["none", "dense", "moe", "moe_shared"])
+        mlp = None if kind == "none" else dense(ff=pick([24, 64, 100])) if kind == "dense" else \
+            moe(experts=pick([2, 3, 8, 16]), top=1, ff=pick([8, 12, 32]), scale=pick([0.5, 1.0, 2.5]), shared_ff=pick([8, 40]) if kind == "moe_shared" else None)
+        if mlp and mlp["kind"] == "moe":
+            mlp["router"]["top"] = pick(list(range(1, mlp["router"]["experts"] + 1)))
+        if mlp and mlp["kind"] == "moe" and not experts:
+            mlp = dense(ff=mlp["expert"]["ff"] * 2)
+        layers.append(layer(m, mlp))
+    return config(layers, width=width, vocab=pick([50, 131, 256]), eps=pick([1e-6, 1e-5]))

@@ -170,7 +170,8 @@ class ZugunexForCausalLM:
     @staticmethod
     def random_weights(config: ZugunexConfig, seed: int = 0) -> Dict[str, torch.Tensor]:
         """Seeded bf16 weights of the right shapes (tests, benchmarks): projections ~ N(0, 1/in), embeddings ~ N(0, 1), norm weights
-        around 1, sinks ~ N(0, 1)."""
+        around 1, sinks ~ N(0, 1); routers ~ N(0, 1/(4 in)), so that router logits stay where an fp32 sigmoid still tells them apart
+        (beyond |z| ~ 17 the scores of different experts round to the same number and the choice falls to the tie rule)."""
         g = torch.Generator().manual_seed(seed)
         out = {}
         for k, shp in config.tensor_shapes().items():
@@ -178,7 +179,7 @@ class ZugunexForCausalLM:
             if leaf == "embed":
                 t = torch.randn(shp, generator=g)
             elif leaf == "router":
-                t = torch.randn(shp, generator=g) * 2.0 / (shp[1] ** 0.5)
+                t = torch.randn(shp, generator=g) * 0.5 / (shp[1] ** 0.5)
             elif len(shp) == 2:
                 t = torch.randn(shp, generator=g) / (shp[1] ** 0.5)
             elif leaf == "sink":
