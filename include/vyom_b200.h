@@ -717,12 +717,12 @@ typedef struct VyWinAttn {
   /* row strides of the two pools in elements; 0 = kv_heads * dim and kv_heads * vdim. With explicit strides k_pool and v_pool
    * may be views of ONE pool (latent attention: the value is the leading part of the key row). */
   int64_t k_row, v_row;
-  /* optional scratch of vy_window_attn_workspace_floats(n_seqs, heads, vdim) floats: single-token steps whose query heads share
+  /* optional scratch of vy_window_attn_workspace_floats(n_seqs, heads, kv_heads, vdim) floats (0: none needed): single-token steps whose query heads share
    * key / value rows in groups of 8 or more split a sequence's keys over several CTAs and combine the parts from here */
   float* workspace; int64_t workspace_floats;
   void* stream;
 } VyWinAttn;
-VY_API int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t vdim);
+VY_API int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t kv_heads, int32_t vdim);
 VY_API int vy_window_attn(const VyWinAttn* p);
 
 /* Depthwise causal convolution over time with carried taps, then an activation:

@@ -850,8 +850,9 @@ extern "C" int vy_kv_page_write(const VyKvWrite* p) {
   return VY_OK;
 }
 
-extern "C" int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t vdim) {
-  return vy::window_attn_heads_workspace_floats(n_seqs, heads, vdim);
+extern "C" int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t kv_heads, int32_t vdim) {
+  if (n_seqs <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || vdim <= 0) return 0;
+  return vy::window_attn_heads_workspace_floats(n_seqs, heads, kv_heads, vdim);
 }
 
 extern "C" int vy_window_attn(const VyWinAttn* p) {

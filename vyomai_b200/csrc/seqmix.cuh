@@ -63,7 +63,7 @@ cudaError_t launch_linear_attn_chunked(const RecDev& d, int n_seqs, cudaStream_t
 cudaError_t launch_window_attn_tiled(const WinDev& d, int n_seqs, int max_new, cudaStream_t st);
 // Single tokens whose query heads share key / value rows in groups of 8 or more (latent rows): heads as the rows of a tile.
 bool window_attn_heads_applies(const WinDev& d);
-long long window_attn_heads_workspace_floats(int n_seqs, int heads, int vdim);
+long long window_attn_heads_workspace_floats(int n_seqs, int heads, int kv_heads, int vdim);
 cudaError_t launch_window_attn_heads(const WinDev& d, int n_seqs, float* ws, long long ws_floats, cudaStream_t st, int* launches);
 
 }  // namespace vy

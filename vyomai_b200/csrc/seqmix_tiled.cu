@@ -657,7 +657,18 @@ constexpr int WH_MIN_HEADS = 8;
 
 bool window_attn_heads_applies(const WinDev& d) { return d.heads / d.kv_heads >= WH_MIN_HEADS && d.dim <= 256 && d.vdim <= 64 * WH_VC; }
 
-long long window_attn_heads_workspace_floats(int n_seqs, int heads, int vdim) { return static_cast<long long>(n_seqs) * heads * 16 * (vdim + 2); }
+// most splits a launch of this geometry can use: enough CTAs for two per SM, never more than 16
+static long long wh_split_bound(int n_seqs, int heads, int kv_heads) {
+  const int per_kv = heads / kv_heads, tiles = (per_kv + WH_H - 1) / WH_H;
+  const long long ctas = static_cast<long long>(n_seqs) * kv_heads * tiles;
+  const long long splits = (2LL * num_sms() + ctas - 1) / ctas;
+  return splits > 16 ? 16 : (splits < 1 ? 1 : splits);
+}
+
+long long window_attn_heads_workspace_floats(int n_seqs, int heads, int kv_heads, int vdim) {
+  const long long splits = wh_split_bound(n_seqs, heads, kv_heads);
+  return splits <= 1 ? 0 : static_cast<long long>(n_seqs) * heads * splits * (vdim + 2);
+}
 
 cudaError_t launch_window_attn_heads(const WinDev& d, int n_seqs, float* ws, long long ws_floats, cudaStream_t st, int* launches) {
   const int dim4 = (d.dim + 3) & ~3, vdim4 = (d.vdim + 3) & ~3;
@@ -677,11 +688,9 @@ cudaError_t launch_window_attn_heads(const WinDev& d, int n_seqs, float* ws, lon
   }
   const int per_kv = d.heads / d.kv_heads, tiles = (per_kv + WH_H - 1) / WH_H;
   // splits: enough CTAs for two per SM, at most one per 64 keys of the longest possible context, at most 16 and what the workspace holds
-  const long long ctas = static_cast<long long>(n_seqs) * d.kv_heads * tiles;
   const long long kmax = d.window > 0 ? static_cast<long long>(d.window) + d.keep : static_cast<long long>(d.tw) * d.bs;
-  long long splits = (2LL * num_sms() + ctas - 1) / ctas;
+  long long splits = wh_split_bound(n_seqs, d.heads, d.kv_heads);
   splits = splits < (kmax + WH_K - 1) / WH_K ? splits : (kmax + WH_K - 1) / WH_K;
-  if (splits > 16) splits = 16;
   if (!ws || ws_floats < static_cast<long long>(n_seqs) * d.heads * splits * (d.vdim + 2)) splits = 1;
   if (splits < 1) splits = 1;
   cudaError_t e = launch_kernel(window_attn_heads_kernel, dim3(static_cast<unsigned>(splits), d.kv_heads * tiles, n_seqs), dim3(WH_T), smem, st, d, ldk,

@@ -1004,7 +1004,8 @@ def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_poo
     out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or q.dtype)
     ws = None
     if batch.max_new == 1 and heads // kv_heads >= 8:   # the heads-as-rows form splits keys over CTAs and merges from a scratch buffer
-        ws = torch.empty(int(_lib.lib().vy_window_attn_workspace_floats(batch.n_seqs, heads, vdim)), device=q.device, dtype=torch.float32)
+        need = int(_lib.lib().vy_window_attn_workspace_floats(batch.n_seqs, heads, kv_heads, vdim))
+        ws = torch.empty(need, device=q.device, dtype=torch.float32) if need > 0 else None
     _lib.call("vy_window_attn", "VyWinAttn", workspace=_ptr(ws), workspace_floats=ws.numel() if ws is not None else 0, q=q.data_ptr(), ldq=q.stride(0), q_dtype=_dt(q), k_pool=k_pool.data_ptr(),
               v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale),
               window=int(window), keep_first=int(keep_first), sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
